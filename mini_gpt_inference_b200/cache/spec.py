@@ -29,6 +29,9 @@ class PagedKVSpec:
     # Queries read only the keys of their own block of this many positions (blocks counted from
     # position 0): the pages of blocks that are over can be given back (None: no such mask).
     block: int | None = None
+    # A token's values are the first ``v_head_dim`` features of its key row: no value pages are kept, attention
+    # reads the values out of the key pages (a latent that serves as both).
+    values_in_keys: bool = False
 
     @property
     def value_dim(self) -> int:
@@ -45,6 +48,8 @@ class PagedKVSpec:
             raise ValueError("page_tokens must be positive when given")
         if self.num_pages is not None and self.num_pages <= 0:
             raise ValueError("num_pages must be positive when given")
+        if self.values_in_keys and self.value_dim > self.head_dim:
+            raise ValueError("values that live in the key rows cannot be longer than a key row")
 
 
 @dataclass(frozen=True)

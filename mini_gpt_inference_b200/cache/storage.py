@@ -26,6 +26,7 @@ class PagedKVView:
     page_tokens: int
     window: int | None
     writes: bool
+    values_in_keys: bool = False   # v_pages is k_pages: a token's values are the first features of its key row
 
 
 @dataclass
@@ -45,7 +46,8 @@ class CacheStorage:
             shape = (len(group.layers), group.num_pages, group.spec.n_kv_head,
                      group.page_tokens, group.spec.head_dim)
             self.k.append(torch.zeros(shape, dtype=dtype, device=self.device))
-            self.v.append(torch.zeros((*shape[:-1], group.spec.value_dim), dtype=dtype, device=self.device))
+            self.v.append(self.k[-1] if group.spec.values_in_keys else
+                          torch.zeros((*shape[:-1], group.spec.value_dim), dtype=dtype, device=self.device))
         self.state: dict[int, torch.Tensor] = {}
         for layer, spec in manager.state_layers.items():
             self.state[layer] = torch.zeros((manager.max_requests, *spec.shape),
@@ -57,7 +59,7 @@ class CacheStorage:
             g = m.group_of_layer[cache_layer]
             idx = m.groups[g].layers.index(cache_layer)
             return PagedKVView(self.k[g][idx], self.v[g][idx], g, m.groups[g].page_tokens,
-                               m.groups[g].spec.window, writes)
+                               m.groups[g].spec.window, writes, m.groups[g].spec.values_in_keys)
         if cache_layer in self.state:
             return StateView(self.state[cache_layer], writes)
         return None
@@ -65,6 +67,6 @@ class CacheStorage:
     def bytes_per_token(self) -> int:
         total = 0
         for g, group in enumerate(self.manager.groups):
-            total += (len(group.layers) * group.spec.n_kv_head
-                      * (group.spec.head_dim + group.spec.value_dim) * self.k[g].element_size())
+            per_head = group.spec.head_dim + (0 if group.spec.values_in_keys else group.spec.value_dim)
+            total += len(group.layers) * group.spec.n_kv_head * per_head * self.k[g].element_size()
         return total

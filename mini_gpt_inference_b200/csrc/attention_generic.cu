@@ -34,7 +34,8 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, int q_stride, const T*
                                T* __restrict__ out, int n_tokens, int n_head, int n_kv_head, int head_dim, int v_dim,
                                const T* __restrict__ gate, int gate_stride,
                                int page_tokens, int max_pages, int window, float scale, int num_pages,
-                               int n_requests, const float* __restrict__ slopes, int block) {
+                               int n_requests, const float* __restrict__ slopes, int block, float softcap,
+                               const float* __restrict__ sinks, int v_stride) {
     extern __shared__ float q_smem[];                     // [WARPS][head_dim]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int token = blockIdx.x;
@@ -79,6 +80,7 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, int q_stride, const T*
             const T* kr = k_pages + (size_t)row * head_dim;
             float dot = 0.f;
             for (int d = 0; d < head_dim; ++d) dot = fmaf(q[d], to_float(kr[d]), dot);
+            if (softcap > 0.f) dot = softcap * tanhf(dot / softcap);
             s = slopes ? dot - slope * (float)(p - j) : dot;
         }
         const float new_max = fmaxf(run_max, warp_max(s));
@@ -92,13 +94,22 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, int q_stride, const T*
         for (int jj = 0; jj < count; ++jj) {
             const float pj = __shfl_sync(0xffffffffu, prob, jj);
             const int rj = __shfl_sync(0xffffffffu, row, jj);
-            const T* vr = v_pages + (size_t)rj * v_dim;
+            const T* vr = v_pages + (size_t)rj * v_stride;
 #pragma unroll
             for (int i = 0; i < MAX_DPL; ++i) {
                 const int d = lane + 32 * i;
                 if (d < v_dim) acc[i] = fmaf(pj, to_float(vr[d]), acc[i]);
             }
         }
+    }
+    if (sinks) {
+        // a sink: one more term exp(sink_h) in the denominator, with no key and no value
+        const float sink = sinks[head];
+        const float new_max = fmaxf(run_max, sink);
+        const float corr = expf(run_max - new_max);
+        run_sum = run_sum * corr + expf(sink - new_max);
+#pragma unroll
+        for (int i = 0; i < MAX_DPL; ++i) acc[i] *= corr;
     }
     const float inv = 1.0f / run_sum;
     T* orow = out + (size_t)token * n_head * v_dim + (size_t)head * v_dim;
@@ -122,7 +133,11 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, int q_stride, const T*
 // values may differ in size); block_table: [n_requests, max_pages]; out: [n_tokens, n_head * v_dim].
 // gate (may be null): rows of `gate_stride` elements whose first n_head * v_dim hold gate values; the
 // output is multiplied by their logistic function.  window <= 0: none.  slopes: [n_head] 32-bit or null;
-// key_block <= 0: no block mask.
+// key_block <= 0: no block mask.  softcap > 0: a score s (scale included) becomes softcap * tanh(s / softcap)
+// before the slopes and the softmax.  sinks: [n_head] 32-bit or null: exp(sink_h) is added to the softmax's
+// denominator of head h (no key, no value; neither scaled nor capped).  v_stride: elements between the value
+// rows of neighbouring tokens in `v_pages` (0: v_dim; larger where a token's values are the first v_dim
+// features of a wider row, its key row for instance).
 // num_pages: pages of the pool (with n_requests, what guarded builds hold the indices against).
 MG_API int mg_paged_attention_general(const void* q, int q_stride, const void* k_pages, const void* v_pages,
                                       const int* block_table, const int* token_request,
@@ -130,8 +145,11 @@ MG_API int mg_paged_attention_general(const void* q, int q_stride, const void* k
                                       int n_kv_head, int head_dim, int v_dim, const void* gate, int gate_stride,
                                       int page_tokens, int max_pages,
                                       int window, float scale, int num_pages, int n_requests, int is_bf16,
-                                      const float* slopes, int key_block, void* stream) {
+                                      const float* slopes, int key_block, float softcap, const float* sinks,
+                                      int v_stride, void* stream) {
     if (n_tokens == 0) return MG_OK;
+    if (v_stride <= 0) v_stride = v_dim;
+    MG_REQUIRE(v_stride >= v_dim && softcap >= 0.f, "attention: bad value stride or cap");
     MG_REQUIRE(n_tokens > 0 && n_head > 0 && n_kv_head > 0 && page_tokens > 0 && max_pages > 0 && key_block >= 0,
                "attention: bad sizes");
     MG_REQUIRE(n_head % n_kv_head == 0, "attention: n_head %d is not a multiple of n_kv_head %d", n_head, n_kv_head);
@@ -147,12 +165,12 @@ MG_API int mg_paged_attention_general(const void* q, int q_stride, const void* k
         paged_attention_generic_kernel<bf16><<<grid, block, smem, s>>>(
             (const bf16*)q, q_stride, (const bf16*)k_pages, (const bf16*)v_pages, block_table, token_request, positions,
             (bf16*)out, n_tokens, n_head, n_kv_head, head_dim, v_dim, (const bf16*)gate, gate_stride, page_tokens,
-            max_pages, window, scale, num_pages, n_requests, slopes, key_block);
+            max_pages, window, scale, num_pages, n_requests, slopes, key_block, softcap, sinks, v_stride);
     else
         paged_attention_generic_kernel<float><<<grid, block, smem, s>>>(
             (const float*)q, q_stride, (const float*)k_pages, (const float*)v_pages, block_table, token_request, positions,
             (float*)out, n_tokens, n_head, n_kv_head, head_dim, v_dim, (const float*)gate, gate_stride, page_tokens,
-            max_pages, window, scale, num_pages, n_requests, slopes, key_block);
+            max_pages, window, scale, num_pages, n_requests, slopes, key_block, softcap, sinks, v_stride);
     MG_CHECK_LAUNCH("paged_attention_generic");
     return MG_OK;
 }
@@ -168,5 +186,5 @@ MG_API int mg_paged_attention_generic(const void* qkv, const void* k_pages, cons
     return mg_paged_attention_general(qkv, (n_head + 2 * n_kv_head) * head_dim, k_pages, v_pages, block_table,
                                       token_request, positions, out, n_tokens, n_head, n_kv_head, head_dim, head_dim,
                                       nullptr, 0, page_tokens, max_pages, window, scale, num_pages, n_requests, is_bf16,
-                                      nullptr, 0, stream);
+                                      nullptr, 0, 0.f, nullptr, 0, stream);
 }

@@ -5,6 +5,9 @@
 //   gated linear attention:  S <- diag(a_t) S + k_t v_t^T,  a_t = sigmoid(z_t)^(1/tau)  (per key channel)
 //   mLSTM:                   m' = max(f_t + m, i_t),  S <- exp(f_t + m - m') S + exp(i_t - m') k_t [v_t, 1]^T,
 //                            i_t = cap tanh(x_i / cap),  f_t = logsigmoid(cap tanh(x_f / cap))
+//   state-space duality (Mamba-2):  S <- exp(-exp(A_h) dt_t) S + dt_t B_t x_t^T,  dt_t = softplus(raw dt_t),
+//                            o_t = S^T C_t + D_h x_t; B and C (in the places of k and q, unscaled) are shared by the
+//                            heads of a group of neighbouring heads, A_h and D_h are one number per head
 //   o_t = S^T q_t,  q_t scaled by head_dim^(-1/2)
 // S is [value column][key channel] in 32-bit in the request's state slot; it starts at zero when the
 // request has nothing in the cache.  For the mLSTM the normaliser n is one more value column (the
@@ -31,19 +34,24 @@ constexpr int THREADS = COLS * DPARTS;
 __device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 
 // DPT: key channels per thread (head_dim <= 4 * DPT; channels beyond head_dim are zeros)
-template <typename T, int DPT, bool MLSTM>
+constexpr int MODE_GLA = 0, MODE_MLSTM = 1, MODE_SSD = 2;
+
+__device__ __forceinline__ float softplus(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
+
+template <typename T, int DPT, int MODE>
 __global__ void __launch_bounds__(THREADS)
 matrix_memory_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int v_off,
                           const float* __restrict__ gates, int gates_ld, const int* __restrict__ req_q_start,
                           const int* __restrict__ req_q_len, const int* __restrict__ req_ctx_before,
                           const int* __restrict__ req_state_slot, float* __restrict__ state, long long state_stride,
                           float* __restrict__ out, float* __restrict__ aux, int n_head, int head_dim, int v_dim,
-                          float constant, int n_slots, int n_tokens) {
+                          float constant, int n_slots, int n_tokens, int qk_group, const float* __restrict__ head_consts) {
+    constexpr bool MLSTM = MODE == MODE_MLSTM, SSD = MODE == MODE_SSD, GLA = MODE == MODE_GLA;
     constexpr int TCHUNK = DPT >= 64 ? 8 : 16;                 // tokens staged at a time (48 KB of shared memory at most)
     constexpr int ROW = DPT + 4;                               // a thread's channels, padded: float4 reads without bank conflicts
     __shared__ __align__(16) float q_s[TCHUNK][DPARTS * ROW];
     __shared__ __align__(16) float k_s[TCHUNK][DPARTS * ROW];
-    __shared__ __align__(16) float a_s[MLSTM ? 1 : TCHUNK][MLSTM ? 4 : DPARTS * ROW];
+    __shared__ __align__(16) float a_s[GLA ? TCHUNK : 1][GLA ? DPARTS * ROW : 4];
     __shared__ float v_s[TCHUNK][COLS];
     __shared__ float gi_s[TCHUNK], gf_s[TCHUNK];
     pdl_trigger();
@@ -72,8 +80,10 @@ matrix_memory_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_o
         S[i] = (!fresh && col_ok && d < head_dim) ? s_base[d] : 0.f;
     }
     float m = (MLSTM && !fresh) ? *m_ptr : 0.f;
-    const float q_scale = 1.0f / sqrtf((float)head_dim);
-    const float inv_tau = MLSTM ? 0.f : 1.0f / constant;
+    const float q_scale = SSD ? 1.0f : 1.0f / sqrtf((float)head_dim);
+    const float inv_tau = GLA ? 1.0f / constant : 0.f;
+    const int hq = h / qk_group;                               // the head whose q and k columns this head reads
+    const float rate = SSD ? expf(head_consts[h]) : 0.f, skip = SSD ? head_consts[n_head + h] : 0.f;
 
     for (int t0 = 0; t0 < q_len; t0 += TCHUNK) {
         const int nt = min(TCHUNK, q_len - t0);
@@ -83,15 +93,15 @@ matrix_memory_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_o
             const size_t token = (size_t)(start + t0 + tt);
             float qv = 0.f, kv = 0.f, av = 1.f;
             if (d < head_dim) {
-                const T* row = proj + token * ld + (size_t)h * head_dim + d;
+                const T* row = proj + token * ld + (size_t)hq * head_dim + d;
                 qv = to_float(row[q_off]) * q_scale;
                 kv = to_float(row[k_off]);
-                if (!MLSTM) av = expf(log_sigmoid(gates[token * gates_ld + (size_t)h * head_dim + d]) * inv_tau);
+                if (GLA) av = expf(log_sigmoid(gates[token * gates_ld + (size_t)h * head_dim + d]) * inv_tau);
             }
             const int at = (d / DPT) * ROW + (d % DPT);
             q_s[tt][at] = qv;
             k_s[tt][at] = kv;
-            if (!MLSTM) a_s[tt][at] = av;
+            if (GLA) a_s[tt][at] = av;
         }
         for (int idx = tid; idx < nt * COLS; idx += THREADS) {
             const int tt = idx / COLS, c = idx - tt * COLS, cg = slice * COLS + c;
@@ -106,6 +116,11 @@ matrix_memory_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_o
             gi_s[tid] = constant * tanhf(g[h] / constant);
             gf_s[tid] = log_sigmoid(constant * tanhf(g[n_head + h] / constant));
         }
+        if (SSD && tid < nt) {
+            const float dt = softplus(gates[(size_t)(start + t0 + tid) * gates_ld + h]);
+            gi_s[tid] = dt;                                    // the step size
+            gf_s[tid] = expf(-rate * dt);                      // what the state keeps over the step
+        }
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
             float keep = 1.f, vv = v_s[tt][col_local];
@@ -116,15 +131,20 @@ matrix_memory_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_o
                 vv *= expf(gi - m_new);
                 m = m_new;
             }
+            const float x_raw = vv;
+            if (SSD) {
+                keep = gf_s[tt];
+                vv *= gi_s[tt];
+            }
             const float4* q4 = reinterpret_cast<const float4*>(&q_s[tt][dpart * ROW]);
             const float4* k4 = reinterpret_cast<const float4*>(&k_s[tt][dpart * ROW]);
-            const float4* a4 = reinterpret_cast<const float4*>(&a_s[MLSTM ? 0 : tt][MLSTM ? 0 : dpart * ROW]);
+            const float4* a4 = reinterpret_cast<const float4*>(&a_s[GLA ? tt : 0][GLA ? dpart * ROW : 0]);
             float acc = 0.f;
 #pragma unroll
             for (int i = 0; i < DPT; i += 4) {
                 const float4 qv = q4[i / 4], kv = k4[i / 4];
                 float4 av = make_float4(keep, keep, keep, keep);
-                if (!MLSTM) av = a4[i / 4];
+                if (GLA) av = a4[i / 4];
                 S[i] = fmaf(av.x, S[i], kv.x * vv);
                 S[i + 1] = fmaf(av.y, S[i + 1], kv.y * vv);
                 S[i + 2] = fmaf(av.z, S[i + 2], kv.z * vv);
@@ -138,7 +158,7 @@ matrix_memory_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_o
             acc += __shfl_xor_sync(0xffffffffu, acc, 2);
             if (dpart == 0 && col_ok) {
                 const size_t token = (size_t)(start + t0 + tt);
-                if (col < v_dim) out[(token * n_head + h) * v_dim + col] = acc;
+                if (col < v_dim) out[(token * n_head + h) * v_dim + col] = SSD ? fmaf(skip, x_raw, acc) : acc;
                 else {
                     aux[(token * n_head + h) * 2] = acc;       // n_t . q_t
                     aux[(token * n_head + h) * 2 + 1] = m;     // m_t
@@ -195,15 +215,16 @@ head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ aux
     }
 }
 
-template <typename T, bool MLSTM>
+template <typename T, int MODE>
 cudaError_t launch_scan(int dpt, dim3 grid, cudaStream_t s, const T* proj, int ld, int q_off, int k_off, int v_off,
                         const float* gates, int gates_ld, const int* q_start, const int* q_len, const int* ctx_before,
                         const int* slots, float* state, long long stride, float* out, float* aux, int n_head,
-                        int head_dim, int v_dim, float constant, int n_slots, int n_tokens) {
+                        int head_dim, int v_dim, float constant, int n_slots, int n_tokens, int qk_group,
+                        const float* head_consts) {
 #define MG_SCAN(D)                                                                                                  \
-    return mg_launch(matrix_memory_scan_kernel<T, D, MLSTM>, grid, dim3(THREADS), 0, s, true, proj, ld, q_off, k_off, \
+    return mg_launch(matrix_memory_scan_kernel<T, D, MODE>, grid, dim3(THREADS), 0, s, true, proj, ld, q_off, k_off,  \
                      v_off, gates, gates_ld, q_start, q_len, ctx_before, slots, state, stride, out, aux, n_head,      \
-                     head_dim, v_dim, constant, n_slots, n_tokens)
+                     head_dim, v_dim, constant, n_slots, n_tokens, qk_group, head_consts)
     switch (dpt) {
         case 4: MG_SCAN(4);
         case 8: MG_SCAN(8);
@@ -216,45 +237,49 @@ cudaError_t launch_scan(int dpt, dim3 grid, cudaStream_t s, const T* proj, int l
 
 }  // namespace
 
-// proj: [n_tokens, ld] rows (bfloat16 if is_bf16 else 32-bit) holding q and k (n_head x head_dim each) and v
-// (n_head x v_dim) at the three column offsets; gates: 32-bit rows of gates_ld numbers: the decays'
-// pre-activations z [n_head x head_dim] (mlstm = 0, constant = tau) or the input and forget gates'
-// pre-activations [2 x n_head] (mlstm = 1, constant = the cap).  req_*: [n_requests] first row, tokens, tokens
-// already in the cache, state slot.  state: [n_slots, state_stride] 32-bit.  out: [n_tokens, n_head * v_dim]
-// 32-bit; aux: [n_tokens, n_head, 2] 32-bit (mlstm only).
+// proj: [n_tokens, ld] rows (bfloat16 if is_bf16 else 32-bit) holding q and k (n_head / qk_group x head_dim each; head
+// h reads those of head h / qk_group) and v (n_head x v_dim) at the three column offsets; gates: 32-bit rows of
+// gates_ld numbers: mode 0 (gated linear attention; constant = tau) the decays' pre-activations z [n_head x head_dim],
+// mode 1 (mLSTM; constant = the cap) the input and forget gates' pre-activations [2 x n_head], mode 2 (state-space
+// duality) the step sizes before their softplus [n_head], with head_consts = [A_0 .. A_(H-1), D_0 .. D_(H-1)] 32-bit on
+// the device.  req_*: [n_requests] first row, tokens, tokens already in the cache, state slot.  state: [n_slots,
+// state_stride] 32-bit.  out: [n_tokens, n_head * v_dim] 32-bit; aux: [n_tokens, n_head, 2] 32-bit (mLSTM only).
 MG_API int mg_matrix_memory_scan(const void* proj, int ld, int q_off, int k_off, int v_off, const float* gates,
                                  int gates_ld, const int* req_q_start, const int* req_q_len, const int* req_ctx_before,
                                  const int* req_state_slot, float* state, long long state_stride, float* out, float* aux,
                                  int n_requests, int n_tokens, int n_head, int head_dim, int v_dim, float constant,
-                                 int mlstm, int n_slots, int is_bf16, void* stream) {
+                                 int mode, int n_slots, int is_bf16, int qk_group, const float* head_consts, void* stream) {
     if (n_requests == 0 || n_tokens == 0) return MG_OK;
     MG_REQUIRE(n_requests > 0 && n_tokens > 0 && n_head > 0 && head_dim > 0 && v_dim > 0 && n_slots > 0,
                "matrix memory: bad sizes");
+    MG_REQUIRE(mode >= 0 && mode <= 2, "matrix memory: mode %d", mode);
     MG_REQUIRE(head_dim <= 256, "matrix memory: heads of up to 256 key channels (got %d)", head_dim);
     MG_REQUIRE(n_head <= 65535 && n_requests <= 65535, "matrix memory: too many heads or requests");
-    MG_REQUIRE(constant > 0.f, "matrix memory: tau and the gates' cap must be positive");
-    const int cols = v_dim + (mlstm ? 1 : 0);
+    MG_REQUIRE(mode == MODE_SSD || constant > 0.f, "matrix memory: tau and the gates' cap must be positive");
+    MG_REQUIRE(qk_group > 0 && n_head % qk_group == 0, "matrix memory: %d heads do not form groups of %d", n_head, qk_group);
+    MG_REQUIRE(mode != MODE_SSD || head_consts != nullptr, "matrix memory: the state-space form wants its per-head constants");
+    const bool mlstm = mode == MODE_MLSTM;
+    const int cols = v_dim + (mlstm ? 1 : 0), qk_heads = n_head / qk_group;
     MG_REQUIRE(state_stride >= (long long)n_head * cols * head_dim + (mlstm ? n_head : 0), "matrix memory: the state slots are too small");
-    MG_REQUIRE(q_off >= 0 && k_off >= 0 && v_off >= 0 && q_off + n_head * head_dim <= ld && k_off + n_head * head_dim <= ld &&
+    MG_REQUIRE(q_off >= 0 && k_off >= 0 && v_off >= 0 && q_off + qk_heads * head_dim <= ld && k_off + qk_heads * head_dim <= ld &&
                    v_off + n_head * v_dim <= ld, "matrix memory: heads outside the rows");
-    MG_REQUIRE(gates_ld >= (mlstm ? 2 * n_head : n_head * head_dim), "matrix memory: the gates' rows are too short");
+    MG_REQUIRE(gates_ld >= (mlstm ? 2 * n_head : mode == MODE_SSD ? n_head : n_head * head_dim), "matrix memory: the gates' rows are too short");
     MG_REQUIRE(!mlstm || aux != nullptr, "matrix memory: the mLSTM wants room for its normaliser");
     const int dpt = head_dim <= 16 ? 4 : head_dim <= 32 ? 8 : head_dim <= 64 ? 16 : head_dim <= 128 ? 32 : 64;
     const dim3 grid(ceil_div(cols, COLS), n_head, n_requests);
     cudaStream_t s = (cudaStream_t)stream;
     cudaError_t e;
-    if (is_bf16 && mlstm)
-        e = launch_scan<bf16, true>(dpt, grid, s, (const bf16*)proj, ld, q_off, k_off, v_off, gates, gates_ld, req_q_start, req_q_len,
-                                    req_ctx_before, req_state_slot, state, state_stride, out, aux, n_head, head_dim, v_dim, constant, n_slots, n_tokens);
-    else if (is_bf16)
-        e = launch_scan<bf16, false>(dpt, grid, s, (const bf16*)proj, ld, q_off, k_off, v_off, gates, gates_ld, req_q_start, req_q_len,
-                                     req_ctx_before, req_state_slot, state, state_stride, out, aux, n_head, head_dim, v_dim, constant, n_slots, n_tokens);
-    else if (mlstm)
-        e = launch_scan<float, true>(dpt, grid, s, (const float*)proj, ld, q_off, k_off, v_off, gates, gates_ld, req_q_start, req_q_len,
-                                     req_ctx_before, req_state_slot, state, state_stride, out, aux, n_head, head_dim, v_dim, constant, n_slots, n_tokens);
+#define MG_SCAN_ARGS(T) dpt, grid, s, (const T*)proj, ld, q_off, k_off, v_off, gates, gates_ld, req_q_start, req_q_len, req_ctx_before, \
+                        req_state_slot, state, state_stride, out, aux, n_head, head_dim, v_dim, constant, n_slots, n_tokens, qk_group, head_consts
+    if (is_bf16)
+        e = mode == MODE_MLSTM ? launch_scan<bf16, MODE_MLSTM>(MG_SCAN_ARGS(bf16))
+          : mode == MODE_SSD   ? launch_scan<bf16, MODE_SSD>(MG_SCAN_ARGS(bf16))
+                               : launch_scan<bf16, MODE_GLA>(MG_SCAN_ARGS(bf16));
     else
-        e = launch_scan<float, false>(dpt, grid, s, (const float*)proj, ld, q_off, k_off, v_off, gates, gates_ld, req_q_start, req_q_len,
-                                      req_ctx_before, req_state_slot, state, state_stride, out, aux, n_head, head_dim, v_dim, constant, n_slots, n_tokens);
+        e = mode == MODE_MLSTM ? launch_scan<float, MODE_MLSTM>(MG_SCAN_ARGS(float))
+          : mode == MODE_SSD   ? launch_scan<float, MODE_SSD>(MG_SCAN_ARGS(float))
+                               : launch_scan<float, MODE_GLA>(MG_SCAN_ARGS(float));
+#undef MG_SCAN_ARGS
     if (e != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "matrix memory scan: %s", cudaGetErrorString(e));
     return MG_OK;
 }

@@ -25,13 +25,22 @@ _SIGNATURES = {
     "mg_scale": [_P, ctypes.c_longlong, _F, _P],
     "mg_head_prepare": [_P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _P],
     "mg_paged_attention_general": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _I, _I, _F,
-                                   _I, _I, _I, _P, _I, _P],
+                                   _I, _I, _I, _P, _I, _F, _P, _I, _P],
+    "mg_streams_read": [_P, _P, _P, _P, _I, ctypes.c_longlong, _P],
+    "mg_streams_write": [_P, _P, _P, _P, _P, _P, _P, _I, ctypes.c_longlong, _P],
+    "mg_streams_spread": [_P, _P, _I, ctypes.c_longlong, _P],
+    "mg_qk_norm_rotary": [_P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P],
+    "mg_latent_prepare": [_P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _F, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
+    "mg_head_linear": [_P, _I, _I, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "mg_causal_conv_silu": [_P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, ctypes.c_longlong, _P, _I, _I, _I, _I, _I, _I, _P],
+    "mg_conv_state_update": [_P, _I, _I, _P, _P, _P, _P, _P, ctypes.c_longlong, _I, _I, _I, _I, _I, _P],
+    "mg_gated_group_norm": [_P, _P, _I, _P, _P, _P, _I, _I, _I, _F, _I, _P],
     "mg_embed_pairs": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I,
                        _I, _I, _P],
     "mg_rmsnorm": [_P, _P, _P, _I, _I, _F, _F, _I, _P],
     "mg_concat_cast": [_P, _P, _P, _I, _I, _I, _P],
     "mg_matrix_memory_scan": [_P, _I, _I, _I, _I, _P, _I, _P, _P, _P, _P, _P, ctypes.c_longlong, _P, _P, _I, _I, _I, _I,
-                              _I, _F, _I, _I, _I, _P],
+                              _I, _F, _I, _I, _I, _I, _P, _P],
     "mg_matrix_memory_chunked": [_P, _I, _I, _I, _I, _P, _I, _P, _P, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _P, _P, _I,
                                  _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "mg_matrix_memory_chunk_tokens": [_I, _I, _I],
@@ -79,7 +88,8 @@ _SIGNATURES = {
 
 # exported readers of the kernel files' index guards: mg_<name>_index_fault(long long[4])
 GUARDED_FILES = ("elementwise", "linear_skinny", "linear_stream", "linear_wide", "linear_cluster", "linear_tc",
-                 "attention_generic", "attention_split", "attention_prefill", "head_prepare", "moe", "attention_mma", "matrix_memory", "matrix_memory_chunked")
+                 "attention_generic", "attention_split", "attention_prefill", "head_prepare", "moe", "attention_mma", "matrix_memory", "matrix_memory_chunked",
+                 "rotary_prepare", "short_conv")
 for _name in GUARDED_FILES:
     _SIGNATURES[f"mg_{_name}_index_fault"] = [_P]
 GUARD_CODES = {1: "token id", 2: "position", 3: "cache row", 4: "page", 5: "request", 6: "row", 7: "token source"}

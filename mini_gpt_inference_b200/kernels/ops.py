@@ -369,25 +369,38 @@ class CudaOps:
         plan.arrays[name + "/requests"] = np.asarray(ranges, dtype=np.int32).reshape(-1, 2)
         plan.signature.append(("memory_chunks", tokens))
 
-    def matrix_memory_scan(self, ctx, mode, proj, q_off, k_off, v_off, n_head, head_dim, v_dim, gates, constant, state):
+    MEMORY_MODES = {"gla": 0, "mlstm": 1, "ssd": 2}
+
+    def matrix_memory_scan(self, ctx, mode, proj, q_off, k_off, v_off, n_head, head_dim, v_dim, gates, constant, state,
+                           state_offset=0, qk_group=1, head_consts=None):
         """The scan of a mixer with a matrix memory over the step's tokens, request by request, from and to
         the requests' state slots.  ``mode`` ``"gla"``: ``gates`` are the decays' pre-activations
         ``[tokens, n_head * head_dim]`` and ``constant`` is tau; ``"mlstm"``: ``gates`` are the input and
         forget gates' pre-activations ``[tokens, 2 * n_head]`` and ``constant`` is their cap.  Returns
         ``(o [tokens, n_head * v_dim] 32-bit, aux)``; ``aux`` (mlstm) holds ``n . q`` and ``m`` per token
-        and head for the division that ``head_norm_gate`` does."""
+        and head for the division that ``head_norm_gate`` does.
+
+        ``"ssd"`` (state-space duality, Mamba-2): ``S <- exp(-exp(A_h) dt) S + dt k v^T``, ``o = S^T q + D_h v`` with
+        ``dt = softplus(gates[:, h])``, q and k unscaled and shared by ``qk_group`` neighbouring heads, and
+        ``head_consts`` = ``[A_0 .. A_(H-1), D_0 .. D_(H-1)]`` (32-bit).  ``state_offset``: where in a slot the
+        memories begin (a mixer may keep something else in front of them)."""
         self._want(proj, None, "projection rows", 2)
         self._want(gates, torch.float32, "gates", 2)
         self._want(state, torch.float32, "state slots", 2)
-        if mode not in ("gla", "mlstm"):
+        if mode not in self.MEMORY_MODES:
             raise KernelLibraryError(f"matrix memory: mode {mode!r}")
+        if mode == "ssd" and (head_consts is None or self._want(head_consts, torch.float32, "per-head constants", 1).numel() != 2 * n_head):
+            raise KernelLibraryError("matrix memory: the state-space form wants A and D of every head")
+        cols_needed = n_head * (v_dim + (1 if mode == "mlstm" else 0)) * head_dim + (n_head if mode == "mlstm" else 0)
+        if state_offset < 0 or state_offset + cols_needed > state.shape[1]:
+            raise KernelLibraryError("matrix memory: the state slots are too small")
         n = proj.shape[0]
         if gates.shape[0] != n:
             raise KernelLibraryError("matrix memory: one row of gates per token")
         mlstm = mode == "mlstm"
         out = torch.empty((n, n_head * v_dim), dtype=torch.float32, device=self.device)
         aux = torch.empty((n, n_head, 2), dtype=torch.float32, device=self.device) if mlstm else None
-        name, tokens = self._memory_chunks_name(head_dim, v_dim, mlstm)
+        name, tokens = self._memory_chunks_name(head_dim, v_dim, mlstm) if mode != "ssd" else (None, 0)
         chunks = getattr(ctx, "extra", {}).get(name) if name is not None else None
         if chunks is not None and chunks.shape[0] > 0 and self.use_chunked_memory:
             # a step with prompt portions: chunk by chunk (three kernels, every SM at work)
@@ -406,9 +419,10 @@ class CudaOps:
             return out, aux
         self._run(self.lib.mg_matrix_memory_scan(
             _ptr(proj), proj.shape[1], q_off, k_off, v_off, _ptr(gates), gates.shape[1], _ptr(ctx.req_q_start),
-            _ptr(ctx.req_q_len), _ptr(ctx.req_ctx_before), _ptr(ctx.req_state_slot), _ptr(state), state.shape[1], _ptr(out),
-            _ptr(aux), ctx.req_q_start.numel(), n, n_head, head_dim, v_dim, float(constant), 1 if mlstm else 0,
-            state.shape[0], self._is_bf16(proj), self._stream()), "matrix memory scan")
+            _ptr(ctx.req_q_len), _ptr(ctx.req_ctx_before), _ptr(ctx.req_state_slot), state.data_ptr() + 4 * int(state_offset),
+            state.shape[1], _ptr(out), _ptr(aux), ctx.req_q_start.numel(), n, n_head, head_dim, v_dim, float(constant),
+            self.MEMORY_MODES[mode], state.shape[0], self._is_bf16(proj), int(qk_group), _ptr(head_consts), self._stream()),
+            "matrix memory scan")
         return out, aux
 
     def head_norm_gate(self, out32, aux, gate, gain, n_head, v_dim, eps, per_head_gain, gate_activation, out_dtype,
@@ -871,13 +885,21 @@ class CudaOps:
         return gain
 
     def paged_attention_general(self, q, n_head, n_kv_head, head_dim, v_dim, scale, cache, ctx, gate=None,
-                                slopes=None, block=None):
+                                slopes=None, block=None, softcap=None, sinks=None):
         """Causal attention of ``q`` (a 2-D tensor whose rows' first ``n_head * head_dim`` columns
         are the queries) over the pages, keys of size ``head_dim`` and values of size ``v_dim``;
         with ``gate`` (a 2-D view, ``n_head * v_dim`` columns) the output is multiplied by the
         logistic function of the gate values.  ``slopes`` (32-bit, one per head): ``slope * (i - j)``
         is taken off the score of query ``i`` and key ``j``; ``block``: a query sees only the keys
-        of its own block of that many positions.  Returns ``[tokens, n_head * v_dim]``."""
+        of its own block of that many positions; ``softcap``: a score ``s`` (scale included) becomes
+        ``softcap * tanh(s / softcap)``; ``sinks`` (32-bit, one per head): ``exp(sink)`` is added to the
+        softmax's denominator.  A cache whose values live in its key rows is read that way.  Returns
+        ``[tokens, n_head * v_dim]``."""
+        if sinks is not None and self._want(sinks, torch.float32, "sinks", 1).numel() != n_head:
+            raise KernelLibraryError("attention: one sink per head")
+        softcap = float(softcap or 0.0)
+        in_keys = bool(getattr(cache, "values_in_keys", False))
+        plain = softcap == 0.0 and sinks is None and not in_keys      # what the tensor-core kernels take
         if slopes is not None and self._want(slopes, torch.float32, "slopes", 1).numel() != n_head:
             raise KernelLibraryError("attention: one slope per head")
         block = int(block or 0)
@@ -891,7 +913,7 @@ class CudaOps:
         out = torch.empty((n, n_head * v_dim), dtype=q.dtype, device=self.device)
         work = getattr(ctx, "extra", {}).get(self._attention_tiles_name(n_head)) if hasattr(ctx, "extra") else None
         if (q.dtype == torch.bfloat16 and work is not None and work.shape[0] > 0 and head_dim == v_dim and not biased
-                and head_dim in self.PREFILL_TC_HEAD_DIMS and self.use_tensor_cores and self.use_prefill_tc
+                and plain and head_dim in self.PREFILL_TC_HEAD_DIMS and self.use_tensor_cores and self.use_prefill_tc
                 and not getattr(ctx, "decode_only", False)):
             # equal key and value sizes that the tcgen05 prompt attention takes: its tiles, with the
             # rows' own width and the gate in its epilogue
@@ -910,7 +932,7 @@ class CudaOps:
             if code != library.UNSUPPORTED:
                 self._run(code, "paged_attention (prefill, tensor cores)")
                 return out
-        if q.dtype == torch.bfloat16 and self.use_tensor_cores and self.use_mma_attention:
+        if q.dtype == torch.bfloat16 and self.use_tensor_cores and self.use_mma_attention and plain:
             # bfloat16: tiles of (token, head) rows on the warp-level tensor cores; single tokens
             # with their keys cut into ranges that a second kernel merges
             single = bool(getattr(ctx, "decode_only", False))
@@ -949,7 +971,179 @@ class CudaOps:
             _ptr(ctx.positions), _ptr(out), n, n_head, n_kv_head, head_dim, v_dim, _ptr(gate),
             gate.stride(0) if gate is not None else 0, cache.page_tokens, table.shape[1], int(cache.window or 0),
             float(scale), cache.k_pages.shape[0], table.shape[0], self._is_bf16(q), _ptr(slopes), block,
-            self._stream()), "paged_attention (general)")
+            softcap, _ptr(sinks), head_dim if in_keys else 0, self._stream()), "paged_attention (general)")
+        return out
+
+    # ---- several residual streams ------------------------------------------------------------------
+    def streams_spread(self, x32, streams):
+        """``[streams, tokens, width]``, every stream a copy of ``x32``."""
+        self._want(x32, torch.float32, "stream", 2)
+        out = torch.empty((int(streams), *x32.shape), dtype=torch.float32, device=self.device)
+        self._run(self.lib.mg_streams_spread(_ptr(x32), _ptr(out), int(streams), x32.numel(), self._stream()), "streams (spread)")
+        return out
+
+    def streams_read(self, streams32, weights, want_zeros=False):
+        """``u = sum_s weights[s] * streams32[s]``; with ``want_zeros`` also a buffer of zeros of u's shape
+        (returns ``(u, zeros)``), into which a sublayer can add its output."""
+        self._want(streams32, torch.float32, "streams", 3)
+        if self._want(weights, torch.float32, "stream weights", 1).numel() != streams32.shape[0]:
+            raise KernelLibraryError("streams: one weight per stream")
+        u = torch.empty(streams32.shape[1:], dtype=torch.float32, device=self.device)
+        zeros = torch.empty_like(u) if want_zeros else None
+        self._run(self.lib.mg_streams_read(_ptr(streams32), _ptr(weights), _ptr(u), _ptr(zeros), streams32.shape[0],
+                                           u.numel(), self._stream()), "streams (read)")
+        return (u, zeros) if want_zeros else u
+
+    def streams_sum(self, streams32):
+        hit = self._packed.get(("stream ones", streams32.shape[0]))
+        if hit is None:
+            hit = self._packed[("stream ones", streams32.shape[0])] = torch.ones(streams32.shape[0], dtype=torch.float32,
+                                                                                device=self.device)
+        return self.streams_read(streams32, hit)
+
+    def streams_write(self, streams32, mix, weights, y32, next_read=None):
+        """In place: ``streams32[t] = sum_s mix[s, t] * streams32[s] + weights[t] * y32`` for all t at once.  With
+        ``next_read`` (the read weights of the sublayer that follows) returns ``(u, zeros)`` as ``streams_read`` of
+        the new streams would."""
+        self._want(streams32, torch.float32, "streams", 3)
+        self._want(y32, torch.float32, "sublayer output", 2)
+        s = streams32.shape[0]
+        if (self._want(mix, torch.float32, "stream mix", 2).shape != (s, s) or y32.shape != streams32.shape[1:]
+                or self._want(weights, torch.float32, "stream weights", 1).numel() != s):
+            raise KernelLibraryError("streams: shapes do not fit")
+        u = zeros = None
+        if next_read is not None:
+            if self._want(next_read, torch.float32, "stream weights", 1).numel() != s:
+                raise KernelLibraryError("streams: one weight per stream")
+            u, zeros = torch.empty_like(y32), torch.empty_like(y32)
+        self._run(self.lib.mg_streams_write(_ptr(streams32), _ptr(mix), _ptr(weights), _ptr(y32), _ptr(next_read), _ptr(u),
+                                            _ptr(zeros), s, y32.numel(), self._stream()), "streams (write)")
+        return (u, zeros) if next_read is not None else None
+
+    # ---- queries and keys that turn with the position ---------------------------------------------------
+    def qk_norm_rotary(self, proj, n_head, n_kv_head, head_dim, v_dim, q_off, k_off, v_off, norm, eps, rot_dims, freq,
+                       cache, slots, positions, q_gain=None, k_gain=None):
+        """Between a fused projection and the attention: optionally one RMS norm over all query features of a
+        token and one over all key features (gains of those whole sizes), then the first ``rot_dims`` features of
+        every query and key head turned by ``position * freq[i]`` (``freq``: 32-bit ``[rot_dims / 2]``); queries in
+        place, keys and values to the cache rows ``slots`` (``cache`` None or read-only: nothing is written)."""
+        self._want(proj, None, "projection rows", 2)
+        self._want(positions, torch.int32, "positions", 1)
+        if rot_dims and self._want(freq, torch.float32, "rotary frequencies", 1).numel() != rot_dims // 2:
+            raise KernelLibraryError("qk_norm_rotary: one frequency per pair of turning features")
+        for gain, size in ((q_gain, n_head * head_dim), (k_gain, n_kv_head * head_dim)):
+            if gain is not None and self._want(gain, torch.float32, "norm gain", 1).numel() != size:
+                raise KernelLibraryError("qk_norm_rotary: a gain does not match its projection")
+        pages = [None, None, None, 0, 0]
+        if cache is not None and cache.writes:
+            self._want(slots, torch.int32, "slot_mapping", 1)
+            self._want(cache.k_pages, proj.dtype, "k_pages", 4)
+            self._want(cache.v_pages, proj.dtype, "v_pages", 4)
+            if (tuple(cache.k_pages.shape[1:]) != (n_kv_head, cache.page_tokens, head_dim)
+                    or tuple(cache.v_pages.shape[1:]) != (n_kv_head, cache.page_tokens, v_dim)):
+                raise KernelLibraryError("qk_norm_rotary: page storage does not match the head sizes")
+            pages = [_ptr(slots), _ptr(cache.k_pages), _ptr(cache.v_pages), cache.page_tokens, cache.k_pages.shape[0]]
+        self._run(self.lib.mg_qk_norm_rotary(
+            _ptr(proj), proj.shape[1], proj.shape[0], n_head, n_kv_head, head_dim, v_dim, q_off, k_off, v_off,
+            1 if norm else 0, float(eps), _ptr(q_gain), _ptr(k_gain), int(rot_dims), _ptr(freq), _ptr(positions), pages[0],
+            pages[1], pages[2], pages[3], pages[4], self._is_bf16(proj), self._stream()), "qk_norm_rotary")
+
+    def latent_prepare(self, proj, n_head, q_off, q_dim, rot_dim, low_off, rank, gain, eps, freq, cache, slots, positions):
+        """For an attention over cached latents.  Returns ``q`` ``[tokens, n_head * (rank + rot_dim)]`` whose last
+        ``rot_dim`` features per head are the turned last ``rot_dim`` features of the query heads in ``proj``
+        (``n_head x (q_dim + rot_dim)`` from ``q_off``); the first ``rank`` per head are left for ``head_linear``.
+        With a writable ``cache``: the ``rank`` numbers of ``proj`` from ``low_off``, RMS-normed with ``gain``, and the
+        ``rot_dim`` behind them, turned, go to the token's cache row."""
+        self._want(proj, None, "projection rows", 2)
+        self._want(positions, torch.int32, "positions", 1)
+        if rot_dim and self._want(freq, torch.float32, "rotary frequencies", 1).numel() != rot_dim // 2:
+            raise KernelLibraryError("latent_prepare: one frequency per pair of turning features")
+        pages = [None, None, None, 0, 0]
+        if cache is not None and cache.writes:
+            self._want(slots, torch.int32, "slot_mapping", 1)
+            self._want(cache.k_pages, proj.dtype, "k_pages", 4)
+            self._want(gain, torch.float32, "latent gain", 1)
+            if tuple(cache.k_pages.shape[1:]) != (1, cache.page_tokens, rank + rot_dim) or gain.numel() != rank:
+                raise KernelLibraryError("latent_prepare: page storage does not match the latent's size")
+            separate = None if getattr(cache, "values_in_keys", False) else self._want(cache.v_pages, proj.dtype, "v_pages", 4)
+            if separate is not None and tuple(separate.shape[1:]) != (1, cache.page_tokens, rank):
+                raise KernelLibraryError("latent_prepare: value pages do not match the latent's size")
+            pages = [_ptr(slots), _ptr(cache.k_pages), _ptr(separate), cache.page_tokens, cache.k_pages.shape[0]]
+        q = torch.empty((proj.shape[0], n_head * (rank + rot_dim)), dtype=proj.dtype, device=self.device)
+        self._run(self.lib.mg_latent_prepare(
+            _ptr(proj), proj.shape[1], proj.shape[0], n_head, q_off, q_dim, int(rot_dim), low_off, rank, _ptr(gain),
+            float(eps), _ptr(freq), _ptr(q), _ptr(positions), pages[0], pages[1], pages[2], pages[3], pages[4],
+            self._is_bf16(proj), self._stream()), "latent_prepare")
+        return q
+
+    def head_linear(self, x, x_off, x_head, weight, rows_are_inputs, n_head, n_in, n_out, gate=None, out=None, out_off=0,
+                    out_head=None):
+        """One small matrix per head: ``out[n, h, j] = sum_i x[n, h, i] * W_h[j, i]`` with ``weight``
+        ``[n_head * n_out, n_in]``, or, with ``rows_are_inputs``, ``sum_i x[n, h, i] * W_h[i, j]`` with ``weight``
+        ``[n_head * n_in, n_out]``.  Head h's inputs are the columns ``x_off + h * x_head ..`` of ``x``; its outputs go
+        to the columns ``out_off + h * out_head ..`` of ``out`` (a new ``[tokens, n_head * n_out]`` tensor unless
+        given).  ``gate`` (a 2-D view, ``n_head * n_out`` columns): the outputs times its logistic function."""
+        self._want(x, weight.dtype, "head inputs", 2)
+        self._want(weight, None, "head matrices", 2)
+        if weight.shape != ((n_head * n_in, n_out) if rows_are_inputs else (n_head * n_out, n_in)):
+            raise KernelLibraryError("head_linear: the matrices do not fit the heads")
+        n = x.shape[0]
+        if gate is not None and (gate.dtype != x.dtype or gate.dim() != 2 or gate.stride(1) != 1
+                                 or gate.shape != (n, n_head * n_out)):
+            raise KernelLibraryError("head_linear: the gate does not fit the heads")
+        if out is None:
+            out, out_off, out_head = torch.empty((n, n_head * n_out), dtype=x.dtype, device=self.device), 0, n_out
+        else:
+            self._want(out, x.dtype, "head outputs", 2)
+            out_head = n_out if out_head is None else out_head
+            if out.shape[0] != n:
+                raise KernelLibraryError("head_linear: one output row per token")
+        self._run(self.lib.mg_head_linear(
+            _ptr(x), x.shape[1], x_off, x_head, _ptr(weight), 1 if rows_are_inputs else 0, _ptr(gate),
+            gate.stride(0) if gate is not None else 0, _ptr(out), out.shape[1], out_off, out_head, n, n_head, n_in, n_out,
+            self._is_bf16(x), self._stream()), "head_linear")
+        return out
+
+    # ---- around the scan of a state-space mixer ---------------------------------------------------------
+    def causal_conv_silu(self, ctx, x, x_off, channels, taps, bias, state):
+        """``silu(bias + causal convolution)`` per channel over every request's tokens (``taps``: 32-bit
+        ``[channels, n]``, the last column weighs the current token); the ``n - 1`` inputs before a step's first
+        token come from the head of the request's state slot.  Returns ``[tokens, channels]`` in x's type."""
+        self._want(x, None, "convolution inputs", 2)
+        self._want(taps, torch.float32, "taps", 2)
+        self._want(state, torch.float32, "state slots", 2)
+        if taps.shape[0] != channels or (bias is not None and self._want(bias, torch.float32, "bias", 1).numel() != channels):
+            raise KernelLibraryError("causal_conv: taps and bias do not fit the channels")
+        out = torch.empty((x.shape[0], channels), dtype=x.dtype, device=self.device)
+        self._run(self.lib.mg_causal_conv_silu(
+            _ptr(x), x.shape[1], x_off, _ptr(taps), _ptr(bias), _ptr(ctx.token_request), _ptr(ctx.positions),
+            _ptr(ctx.req_q_start), _ptr(ctx.req_ctx_before), _ptr(ctx.req_state_slot), _ptr(state), state.shape[1], _ptr(out),
+            x.shape[0], channels, taps.shape[1], ctx.req_q_start.numel(), state.shape[0], self._is_bf16(x), self._stream()),
+            "causal_conv")
+        return out
+
+    def conv_state_update(self, ctx, x, x_off, channels, n_taps, state):
+        """After ``causal_conv_silu`` of the same step: the last ``n_taps - 1`` inputs of every request's sequence go
+        to the head of its state slot."""
+        if n_taps <= 1:
+            return
+        self._run(self.lib.mg_conv_state_update(
+            _ptr(x), x.shape[1], x_off, _ptr(ctx.req_q_start), _ptr(ctx.req_q_len), _ptr(ctx.req_ctx_before),
+            _ptr(ctx.req_state_slot), _ptr(state), state.shape[1], ctx.req_q_start.numel(), channels, int(n_taps),
+            state.shape[0], self._is_bf16(x), self._stream()), "conv_state_update")
+
+    def gated_group_norm(self, out32, gate, gain, parts, eps, out_dtype, positions=None):
+        """``rms_norm(out32 * silu(gate))`` taken over ``parts`` equal parts of a row apart, times ``gain``."""
+        self._want(out32, torch.float32, "scan output", 2)
+        self._want(gain, torch.float32, "norm gain", 1)
+        n, width = out32.shape
+        if (gate.dtype != out_dtype or gate.dim() != 2 or gate.stride(1) != 1 or gate.shape != (n, width)
+                or gain.numel() != width or width % parts):
+            raise KernelLibraryError("gated_group_norm: shapes do not fit")
+        out = torch.empty((n, width), dtype=out_dtype, device=self.device)
+        self._run(self.lib.mg_gated_group_norm(_ptr(out32), _ptr(gate), gate.stride(0), _ptr(gain), _ptr(positions), _ptr(out),
+                                               n, width, int(parts), float(eps), self._is_bf16(out), self._stream()),
+                  "gated_group_norm")
         return out
 
     # ---- routed experts ---------------------------------------------------------------------------

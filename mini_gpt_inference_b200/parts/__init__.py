@@ -1,5 +1,5 @@
-from . import (attention, block, embedding, gated_attention, layernorm, loop_entry, matrix_memory, mlp, moe,  # noqa: F401  (register)
-               positions, rmsnorm)
+from . import (attention, block, embedding, gated_attention, latent_attention, layernorm, loop_entry, matrix_memory, mlp, moe,  # noqa: F401  (register)
+               positions, rmsnorm, stream_connection)
 from .base import (ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS,
                    POSITION_ENCODINGS, FeedForward, Mixer, Norm, Part, PositionEncoding,
                    register_arrangement, register_embedding, register_feed_forward,

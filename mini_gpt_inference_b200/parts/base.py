@@ -21,6 +21,8 @@ Interfaces (what a new part must provide):
 * StreamEntry:      ``forward(ctx, x32, embedded32, index) -> x32``  a transformation of the whole residual
                     stream between layers (the re-entry of a loop over layers), given the embedding's output
                     and the number of the pass that begins; it returns a tensor of its own (never ``embedded32``)
+* Connection:       how a sublayer reads from and writes to several residual streams side by side
+                    (``read(ctx, streams32) -> (u, zeros)``, ``write(ctx, streams32, y32, then=None)``)
 * Block arrangement: a function ``run(ctx, layer, cache, residual32)`` that wires the layer's
                     named parts and returns the tensor that holds the stream (None: in place).
 """
@@ -107,6 +109,16 @@ class StreamEntry(Part):
         raise NotImplementedError
 
 
+class Connection(Part):
+    """What stands between a sublayer and the residual streams of a model that carries several."""
+
+    def read(self, ctx, streams32):
+        raise NotImplementedError
+
+    def write(self, ctx, streams32, y32, then=None):
+        raise NotImplementedError
+
+
 class Registry:
     def __init__(self, role: str) -> None:
         self.role = role
@@ -145,6 +157,7 @@ ARRANGEMENTS = Registry("block arrangement")
 EMBEDDINGS = Registry("embedding")
 HEADS = Registry("output head")
 STREAM_ENTRIES = Registry("stream entry")
+CONNECTIONS = Registry("stream connection")
 
 register_norm = NORMS.register
 register_position_encoding = POSITION_ENCODINGS.register
@@ -154,3 +167,4 @@ register_arrangement = ARRANGEMENTS.register
 register_embedding = EMBEDDINGS.register
 register_head = HEADS.register
 register_stream_entry = STREAM_ENTRIES.register
+register_connection = CONNECTIONS.register

@@ -25,6 +25,16 @@ their norm); ``slope_rate`` (a distance bias: ``slope_h * (i - j)`` is taken off
 only the keys of its own block of that many positions, blocks counted from position 0: the cache
 gives back the pages of blocks that are over).
 
+More variants, again parameters: ``bias`` may also name which of the projections have biases (a tuple out of
+``"q"``, ``"k"``, ``"v"``, ``"out"``); ``norm_scope="projection"`` (one RMS norm over all query features of a
+token at once and one over all key features, before they are split into heads, with gains of those whole sizes
+named ``q.norm`` and ``k.norm``); ``rot_dims`` and ``rot_base`` (rotary positions: the first ``rot_dims`` features
+of every query and key head turn with the token's position, feature ``i`` paired with ``i + rot_dims / 2``, by the
+angle ``position * rot_base ** (-2 i / rot_dims)``, after the norm; the rest pass unchanged); ``softcap`` (a
+score ``s``, scale included, becomes ``softcap * tanh(s / softcap)``); ``sink`` (a learned number per head, named
+``sink``, whose exponential is added to the softmax's denominator: it has no key and no value and is neither
+scaled nor capped).
+
 Positions do not enter otherwise unless the model's position encoding rotates q and k.  The four
 matrices are stored apart in the checkpoint (``q``, ``k``, ``v``, ``g``, then ``o`` and the
 scalar ``vmix``, under names given by ``names``) and joined once when they are bound.
@@ -56,7 +66,8 @@ class GatedUnitAttention(Mixer):
                  cache_page_tokens: int | None = None, cache_pages: int | None = None,
                  names: dict | None = None, position=None, bias: bool = False, norm_weights: bool = False,
                  values: str = "projected", slope_rate: float | None = None, block_mask: int | None = None,
-                 init: str = "normal") -> None:
+                 init: str = "normal", norm_scope: str = "head", rot_dims: int = 0, rot_base: float = 10000.0,
+                 softcap: float | None = None, sink: bool = False) -> None:
         super().__init__(prefix)
         self.width, self.n_head, self.head_dim = width, n_head, head_dim
         self.n_kv_head = n_head if n_kv_head is None else n_kv_head
@@ -77,7 +88,26 @@ class GatedUnitAttention(Mixer):
             raise ValueError("values that are the keys have the keys' size and are not blended")
         if norm_weights and not unit_norm:
             raise ValueError("norm_weights without unit_norm")
-        self.has_bias, self.has_norm_weights, self.values_are_keys = bool(bias), bool(norm_weights), values == "keys"
+        # which projections have biases: True means the queries', the keys' and the output's
+        self.biased = ("q", "k", "out") if bias is True else tuple(bias or ())
+        if any(b not in ("q", "k", "v", "out") for b in self.biased):
+            raise ValueError(f"bias {bias!r}: True, or some of 'q', 'k', 'v', 'out'")
+        if norm_scope not in ("head", "projection"):
+            raise ValueError(f"norm_scope {norm_scope!r}: 'head' or 'projection'")
+        if rot_dims < 0 or rot_dims % 2 or rot_dims > head_dim:
+            raise ValueError(f"rot_dims {rot_dims}: an even number of at most head_dim ({head_dim}) features")
+        self.norm_scope, self.rot_dims, self.rot_base = norm_scope, int(rot_dims), float(rot_base)
+        # queries and keys that turn with the position, or are normed across heads, go through another kernel
+        self.turns = self.rot_dims > 0 or norm_scope == "projection"
+        if self.turns and (value_blend is not None or values == "keys" or (unit_norm and not norm_weights
+                                                                           and norm_scope == "projection")):
+            raise ValueError("rotary positions and the projection-wide norm go with projected, unblended values "
+                             "and with gains on the norm")
+        if self.turns and unit_norm and norm_scope == "head":
+            raise ValueError("rotary positions go with the projection-wide norm or with none")
+        self.softcap = None if softcap is None else float(softcap)
+        self.has_sink = bool(sink)
+        self.has_bias, self.has_norm_weights, self.values_are_keys = bool(self.biased), bool(norm_weights), values == "keys"
         self.slope_rate = None if slope_rate is None else float(slope_rate)
         self.block_mask = block_mask
         self._init = init
@@ -94,7 +124,7 @@ class GatedUnitAttention(Mixer):
         else:
             self.g_off = self.v_off + self.v_width
         self.fused_weight = self.out_weight = self.blend = None
-        self.fused_bias = self.out_bias = self.q_gain = self.k_gain = self.slopes = None
+        self.fused_bias = self.out_bias = self.q_gain = self.k_gain = self.slopes = self.sinks = self.freq = None
 
     def _name(self, which: str) -> str:
         return self.prefix + self.names[which]
@@ -108,13 +138,17 @@ class GatedUnitAttention(Mixer):
         }
         if not self.values_are_keys:
             specs[self._name("v")] = TensorSpec((self.v_width, self.width), "matrix", init)
-        if self.has_bias:
-            specs[self._name("q") + ".b"] = TensorSpec((self.q_width,), "vector", "norm_shift")
-            specs[self._name("k") + ".b"] = TensorSpec((self.k_width,), "vector", "norm_shift")
+        for which, size in (("q", self.q_width), ("k", self.k_width), ("v", self.v_width)):
+            if which in self.biased:
+                specs[self._name(which) + ".b"] = TensorSpec((size,), "vector", "norm_shift")
+        if "out" in self.biased:
             specs[self._name("out") + ".b"] = TensorSpec((self.width,), "vector", "bias")
         if self.has_norm_weights:
-            specs[self._name("q") + ".norm"] = TensorSpec((self.head_dim,), "vector", "norm_gain")
-            specs[self._name("k") + ".norm"] = TensorSpec((self.head_dim,), "vector", "norm_gain")
+            whole = self.norm_scope == "projection"
+            specs[self._name("q") + ".norm"] = TensorSpec((self.q_width if whole else self.head_dim,), "vector", "norm_gain")
+            specs[self._name("k") + ".norm"] = TensorSpec((self.k_width if whole else self.head_dim,), "vector", "norm_gain")
+        if self.has_sink:
+            specs[self.prefix + self.names.get("sink", "sink")] = TensorSpec((self.n_head,), "vector", "unit_normal")
         if self.has_gate:
             specs[self._name("gate")] = TensorSpec((self.o_width, self.width), "matrix")
         if self.value_blend is not None or self.has_blend_tensor:
@@ -131,11 +165,19 @@ class GatedUnitAttention(Mixer):
         self.fused_weight = torch.cat(rows, dim=0).contiguous() if all(r is not None for r in rows) else None
         self.out_weight = tensors.get(self._name("out"))
         if self.has_bias and self.fused_weight is not None:
-            qb, kb = tensors.get(self._name("q") + ".b"), tensors.get(self._name("k") + ".b")
-            self.fused_bias = torch.zeros(self.fused_weight.shape[0], dtype=torch.float32, device=self.fused_weight.device)
-            self.fused_bias[: self.q_width] = qb
-            self.fused_bias[self.k_off: self.k_off + self.k_width] = kb
-            self.out_bias = tensors.get(self._name("out") + ".b")
+            if any(b in self.biased for b in ("q", "k", "v")):
+                self.fused_bias = torch.zeros(self.fused_weight.shape[0], dtype=torch.float32, device=self.fused_weight.device)
+                for which, off, size in (("q", 0, self.q_width), ("k", self.k_off, self.k_width), ("v", self.v_off, self.v_width)):
+                    if which in self.biased:
+                        self.fused_bias[off: off + size] = tensors.get(self._name(which) + ".b")
+            if "out" in self.biased:
+                self.out_bias = tensors.get(self._name("out") + ".b")
+        if self.has_sink:
+            self.sinks = tensors.get(self.prefix + self.names.get("sink", "sink"))
+        if self.rot_dims and self.out_weight is not None:
+            # f_i = base^(-2 i / n), worked out in 64-bit and handed to the kernel as 32-bit numbers
+            freq = [self.rot_base ** (-2.0 * i / self.rot_dims) for i in range(self.rot_dims // 2)]
+            self.freq = torch.tensor(freq, dtype=torch.float64).to(dtype=torch.float32, device=self.out_weight.device)
         if self.has_norm_weights:
             self.q_gain, self.k_gain = tensors.get(self._name("q") + ".norm"), tensors.get(self._name("k") + ".norm")
         if self.slope_rate is not None and self.out_weight is not None:
@@ -153,7 +195,8 @@ class GatedUnitAttention(Mixer):
         # where keys and values have one size, the kernel set may cut prompt portions into the tiles of
         # its tiled attention kernel (the same work list as the plain causal attention's)
         planner = getattr(ops, "plan_prompt_attention", None)
-        if planner is not None and self.head_dim == self.v_head_dim and self.slopes is None and self.block_mask is None:
+        if (planner is not None and self.head_dim == self.v_head_dim and self.slopes is None and self.block_mask is None
+                and self.softcap is None and not self.has_sink):
             planner(batch, plan, self.n_head, self.n_kv_head, self.head_dim)
 
     def forward(self, ctx, cache, y, residual32) -> None:
@@ -172,15 +215,24 @@ class GatedUnitAttention(Mixer):
         elif self.value_blend == "source":
             ctx.shared[VALUE_SOURCE] = proj[:, self.v_off: self.v_off + self.v_width]
         extra = {"q_gain": self.q_gain, "k_gain": self.k_gain} if self.has_norm_weights else {}
-        ops.head_prepare(proj, self.n_head, self.n_kv_head, self.head_dim, self.v_head_dim, 0, self.k_off,
-                         self.v_off, self.unit_norm, self.eps, cache, ctx.slot_mapping[cache.group],
-                         ctx.positions, v_other=other, blend=blend, **extra)
+        if self.turns:
+            ops.qk_norm_rotary(proj, self.n_head, self.n_kv_head, self.head_dim, self.v_head_dim, 0, self.k_off,
+                               self.v_off, self.unit_norm, self.eps, self.rot_dims, self.freq, cache,
+                               ctx.slot_mapping[cache.group], ctx.positions, **extra)
+        else:
+            ops.head_prepare(proj, self.n_head, self.n_kv_head, self.head_dim, self.v_head_dim, 0, self.k_off,
+                             self.v_off, self.unit_norm, self.eps, cache, ctx.slot_mapping[cache.group],
+                             ctx.positions, v_other=other, blend=blend, **extra)
         gate = proj[:, self.g_off: self.g_off + self.o_width] if self.has_gate else None
         extra = {}
         if self.slopes is not None:
             extra["slopes"] = self.slopes
         if self.block_mask is not None:
             extra["block"] = self.block_mask
+        if self.softcap is not None:
+            extra["softcap"] = self.softcap
+        if self.sinks is not None:
+            extra["sinks"] = self.sinks
         out = ops.paged_attention_general(proj, self.n_head, self.n_kv_head, self.head_dim, self.v_head_dim,
                                           self.scale, cache, ctx, gate=gate, **extra)
         ops.linear_residual(out, self.out_weight, self.out_bias, residual32)

@@ -160,3 +160,80 @@ class MLSTM(_MatrixMemoryMixer):
         out, aux = ops.matrix_memory_scan(ctx, "mlstm", proj, 0, self.k_off, self.v_off, self.n_head, self.head_dim,
                                           self.v_head_dim, gates, self.gate_cap, cache.state)
         self._finish(ctx, proj, out, aux, residual32, True, "sigmoid")
+
+
+@register_mixer("state_space_duality")
+class StateSpaceDuality(Mixer):
+    """Mamba-2: a matrix memory per head with one scalar decay per head and step, ``inner = n_head * v_head_dim``.
+
+    ``W_in h`` is ``[z: inner | x: inner | B: groups * state | C: groups * state | dt: n_head]``.  ``x``, ``B`` and ``C``
+    together pass a causal convolution per channel (``conv`` ``[channels, taps]``, the last tap weighs the current
+    token, zeros before the sequence's start; bias ``conv.b``) and silu.  ``dt <- softplus(dt + dt_bias)``.  Per head
+    (head ``a`` uses the B and C of group ``a // (n_head / groups)``): ``S_t = exp(-exp(A_log_a) dt) S_(t-1) + dt B_t
+    x_t^T`` (``state x v_head_dim``), ``y_t = S_t^T C_t + D_a x_t``.  The concatenated heads times ``silu(z)`` are
+    RMS-normed in ``norm_groups`` equal parts, each by its own root mean square, times ``norm``, and projected.
+
+    A request's state slot holds the last ``taps - 1`` inputs of the convolution (32-bit), then the memories.  The
+    step sizes come from a projection of their own that writes 32-bit; softplus, decays, the memories and the norm
+    are 32-bit whatever the compute dtype.
+    """
+
+    graph_safe = True      # launches kernels only; the state slot and the token counts are read on the device
+    accepts_deferred_norm = True
+
+    def __init__(self, prefix: str, width: int, n_head: int, v_head_dim: int, state: int, groups: int, taps: int,
+                 norm_groups: int, eps: float, position=None) -> None:
+        super().__init__(prefix)
+        if n_head % groups or (n_head * v_head_dim) % norm_groups:
+            raise ValueError("heads must form equal groups, and their features equal parts for the norm")
+        self.width, self.n_head, self.v_head_dim, self.state, self.groups = width, n_head, v_head_dim, state, groups
+        self.taps, self.norm_groups, self.eps = taps, norm_groups, float(eps)
+        self.inner = n_head * v_head_dim
+        self.channels = self.inner + 2 * groups * state          # what passes the convolution: [x | B | C]
+        self.conv_state = (taps - 1) * self.channels
+        self.main_weight = self.step_weight = self.step_bias = self.out_weight = None
+        self.conv_taps = self.conv_bias = self.head_consts = self.norm_gain = None
+
+    def tensor_specs(self):
+        p, c = self.prefix, self.width
+        return {p + "in": TensorSpec((self.inner + self.channels + self.n_head, c), "matrix", "fan_in"),
+                p + "conv": TensorSpec((self.channels, self.taps), "vector", "fan_in"),
+                p + "conv.b": TensorSpec((self.channels,), "vector", "norm_shift"),
+                p + "dt_bias": TensorSpec((self.n_head,), "vector", "unit_normal"),
+                p + "A_log": TensorSpec((self.n_head,), "vector", "unit_normal"),
+                p + "D": TensorSpec((self.n_head,), "vector", "norm_gain"),
+                p + "norm": TensorSpec((self.inner,), "vector", "norm_gain"),
+                p + "o": TensorSpec((c, self.inner), "matrix", "fan_in_residual")}
+
+    def bind(self, tensors) -> None:
+        p = self.prefix
+        w_in = tensors.get(p + "in")
+        if w_in is None:
+            return
+        split = self.inner + self.channels
+        # the step sizes get a projection of their own: it writes 32-bit and adds dt_bias on its way
+        self.main_weight, self.step_weight = w_in[:split].contiguous(), w_in[split:].contiguous()
+        self.step_bias = tensors[p + "dt_bias"]
+        self.conv_taps, self.conv_bias = tensors[p + "conv"], tensors[p + "conv.b"]
+        self.head_consts = torch.cat([tensors[p + "A_log"], tensors[p + "D"]]).contiguous()
+        self.norm_gain, self.out_weight = tensors[p + "norm"], tensors[p + "o"]
+
+    def cache_spec(self):
+        return FixedStateSpec((self.conv_state + self.n_head * self.v_head_dim * self.state,), "float32")
+
+    def forward(self, ctx, cache, y, residual32) -> None:
+        ops = ctx.ops
+        if hasattr(y, "materialize"):
+            y = y.materialize()                      # two projections read the normalised rows
+        proj = ops.linear(y, self.main_weight, None, "none", ctx.act_dtype)              # [z | x | B | C]
+        steps = ops.linear(y, self.step_weight, self.step_bias, "none", torch.float32)   # dt + dt_bias
+        xbc = ops.causal_conv_silu(ctx, proj, self.inner, self.channels, self.conv_taps, self.conv_bias, cache.state)
+        ops.conv_state_update(ctx, proj, self.inner, self.channels, self.taps, cache.state)
+        b_off = self.inner
+        out, _ = ops.matrix_memory_scan(ctx, "ssd", xbc, b_off + self.groups * self.state, b_off, 0, self.n_head,
+                                        self.state, self.v_head_dim, steps, 0.0, cache.state,
+                                        state_offset=self.conv_state, qk_group=self.n_head // self.groups,
+                                        head_consts=self.head_consts)
+        heads = ops.gated_group_norm(out, proj[:, : self.inner], self.norm_gain, self.norm_groups, self.eps,
+                                     ctx.act_dtype, positions=ctx.positions)
+        ops.linear_residual(heads, self.out_weight, None, residual32)

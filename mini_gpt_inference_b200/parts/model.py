@@ -10,7 +10,7 @@ from __future__ import annotations
 
 from typing import Any, Mapping
 
-from .base import (ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS,
+from .base import (ARRANGEMENTS, CONNECTIONS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS,
                    POSITION_ENCODINGS, STREAM_ENTRIES)
 from .block import Layer, stream_after
 from .spec import ModelSpec, TensorSpec
@@ -30,7 +30,8 @@ class DecoderModel:
                 if role == "mixer":
                     parts[name] = MIXERS.build(part_spec, p, position=self.position)
                 else:
-                    parts[name] = (NORMS if role == "norm" else FEED_FORWARDS).build(part_spec, p)
+                    registry = {"norm": NORMS, "feed_forward": FEED_FORWARDS, "connection": CONNECTIONS}[role]
+                    parts[name] = registry.build(part_spec, p)
             self.layers.append(Layer(parts, roles, ARRANGEMENTS.get(layer_spec.arrangement), p))
         self.entries = [STREAM_ENTRIES.build(entry, "") for entry in spec.entries]
         self.final_norm = NORMS.build(spec.final_norm, "")
@@ -93,6 +94,8 @@ class DecoderModel:
             x = self.embedding.forward(ctx, self.position)
         # layers add into the stream in place: what a stream entry wants of the embedding's output is a copy
         x_embedded = ctx.ops.clone(x) if self.entries else None
+        if self.spec.streams is not None:
+            x = ctx.ops.streams_spread(x, self.spec.streams)          # [streams, tokens, width]
         for call in self.layer_order:
             layer = self.layers[call.layer]
             if call.enter is not None:
@@ -100,6 +103,8 @@ class DecoderModel:
             x = stream_after(layer.run(ctx, layer, ctx.cache_view(call.cache_layer, call.writes_cache), x), x)
         if ctx.logit_rows.numel() == 0:
             return None
+        if self.spec.streams is not None:
+            x = ctx.ops.streams_sum(x)
         if getattr(self.head, "accepts_deferred_norm", False):
             return self.head.forward(ctx, self.final_norm.defer(ctx, x, ctx.logit_rows))
         rows = ctx.ops.gather_rows(x, ctx.logit_rows)

@@ -12,7 +12,7 @@ from dataclasses import dataclass, field
 from typing import Any, Mapping
 
 
-ROLES = ("norm", "mixer", "feed_forward")
+ROLES = ("norm", "mixer", "feed_forward", "connection")
 
 
 @dataclass(frozen=True)
@@ -20,7 +20,7 @@ class PartSpec:
     kind: str                               # key in the part registry of its role
     params: Mapping[str, Any] = field(default_factory=dict)
     name: str = ""                          # weight-name prefix inside its parent ("ln1", "attn")
-    role: str = ""                          # inside a layer: "norm" | "mixer" | "feed_forward"; if empty,
+    role: str = ""                          # inside a layer: "norm" | "mixer" | "feed_forward" | "connection"; if empty,
                                             # taken from the part's name in the layer (see LayerSpec)
 
 
@@ -79,6 +79,8 @@ class ModelSpec:
     final_norm: PartSpec
     head: PartSpec
     n_caches: int | None = None             # cache entries that layer_order names (None: one per layer)
+    streams: int | None = None              # residual streams side by side (None: one stream, handed on as it is);
+                                            # the embedding's output is copied into each, their sum feeds the final norm
     entries: tuple[PartSpec, ...] = ()      # stream-entry parts that layer_order's ``enter`` names
 
     @property

@@ -49,6 +49,8 @@ def random_tensors(model: DecoderModel, seed: int, dtype: torch.dtype = torch.fl
             t = noise / math.sqrt(spec.init_shape[-1] * 2 * n_layer)
         elif spec.init == "unit_normal":
             t = noise
+        elif spec.init == "near_identity":           # a square matrix that mixes a little
+            t = torch.eye(spec.init_shape[0]) + 0.1 * noise
         else:  # "normal", "bias"
             t = 0.02 * noise
         out[name] = t.to(dtype)
