@@ -1,10 +1,11 @@
 from .engine_config import EngineConfig, SamplingParams, canonical_dtype
 from .fakilorn_config import FakilornConfig
 from .model_config import ConfigError, GPTConfig, read_config_json
+from .nukodra_config import NukodraConfig
 from .zenedra_config import ZenedraConfig
 from .registry import (MODEL_REGISTRY, ModelFamily, UnknownArchitectureError, architecture_name,
                        load_config, lookup, register_model)
 
 __all__ = ["EngineConfig", "SamplingParams", "canonical_dtype", "ConfigError", "FakilornConfig", "GPTConfig",
-           "read_config_json", "ZenedraConfig", "MODEL_REGISTRY", "ModelFamily", "UnknownArchitectureError",
+           "read_config_json", "NukodraConfig", "ZenedraConfig", "MODEL_REGISTRY", "ModelFamily", "UnknownArchitectureError",
            "architecture_name", "load_config", "lookup", "register_model"]

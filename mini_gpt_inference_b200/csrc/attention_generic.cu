@@ -12,8 +12,8 @@
 // position 0 of the sequence); `slopes` (one number per head) takes slope_h * (p - j) off the score
 // of key j.
 //
-// Any head_dim up to 256 and any number of heads and kv heads (n_head a multiple of
-// n_kv_head) are accepted.  Entries of the block table are read only for positions lo..p, so
+// Any key size up to 1,024 and value size up to 512 and any number of heads and kv heads (n_head a
+// multiple of n_kv_head) are accepted.  Entries of the block table are read only for positions lo..p, so
 // stale or missing pages elsewhere never matter.
 #include <math.h>
 
@@ -24,9 +24,10 @@ MG_GUARD_DECLARE(attention_generic)
 namespace {
 
 constexpr int WARPS = 4;
-constexpr int MAX_DPL = 8;   // head_dim <= 256: at most 8 dims per lane
+constexpr int MAX_KEY_DIM = 1024;   // a warp's query in shared memory
+constexpr int MAX_VALUE_DIM = 512;  // value features per lane: 8 (values of up to 256) or 16
 
-template <typename T>
+template <typename T, int MAX_DPL>
 __global__ void __launch_bounds__(32 * WARPS)
 paged_attention_generic_kernel(const T* __restrict__ qkv, int q_stride, const T* __restrict__ k_pages,
                                const T* __restrict__ v_pages, const int* __restrict__ block_table,
@@ -153,24 +154,25 @@ MG_API int mg_paged_attention_general(const void* q, int q_stride, const void* k
     MG_REQUIRE(n_tokens > 0 && n_head > 0 && n_kv_head > 0 && page_tokens > 0 && max_pages > 0 && key_block >= 0,
                "attention: bad sizes");
     MG_REQUIRE(n_head % n_kv_head == 0, "attention: n_head %d is not a multiple of n_kv_head %d", n_head, n_kv_head);
-    MG_REQUIRE(head_dim > 0 && head_dim <= 32 * MAX_DPL, "attention: head_dim %d is outside 1..%d", head_dim, 32 * MAX_DPL);
-    MG_REQUIRE(v_dim > 0 && v_dim <= 32 * MAX_DPL, "attention: value size %d is outside 1..%d", v_dim, 32 * MAX_DPL);
+    MG_REQUIRE(head_dim > 0 && head_dim <= MAX_KEY_DIM, "attention: head_dim %d is outside 1..%d", head_dim, MAX_KEY_DIM);
+    MG_REQUIRE(v_dim > 0 && v_dim <= MAX_VALUE_DIM, "attention: value size %d is outside 1..%d", v_dim, MAX_VALUE_DIM);
     MG_REQUIRE(q_stride >= n_head * head_dim && (gate == nullptr || gate_stride >= n_head * v_dim),
                "attention: rows shorter than their heads");
     MG_REQUIRE(ceil_div(n_head, WARPS) <= 65535, "attention: too many heads");
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_tokens, ceil_div(n_head, WARPS)), block(32 * WARPS);
     const size_t smem = (size_t)WARPS * head_dim * sizeof(float);
-    if (is_bf16)
-        paged_attention_generic_kernel<bf16><<<grid, block, smem, s>>>(
-            (const bf16*)q, q_stride, (const bf16*)k_pages, (const bf16*)v_pages, block_table, token_request, positions,
-            (bf16*)out, n_tokens, n_head, n_kv_head, head_dim, v_dim, (const bf16*)gate, gate_stride, page_tokens,
-            max_pages, window, scale, num_pages, n_requests, slopes, key_block, softcap, sinks, v_stride);
-    else
-        paged_attention_generic_kernel<float><<<grid, block, smem, s>>>(
-            (const float*)q, q_stride, (const float*)k_pages, (const float*)v_pages, block_table, token_request, positions,
-            (float*)out, n_tokens, n_head, n_kv_head, head_dim, v_dim, (const float*)gate, gate_stride, page_tokens,
-            max_pages, window, scale, num_pages, n_requests, slopes, key_block, softcap, sinks, v_stride);
+#define MG_LAUNCH_GENERIC(T, DPL)                                                                                       \
+    paged_attention_generic_kernel<T, DPL><<<grid, block, smem, s>>>(                                                   \
+        (const T*)q, q_stride, (const T*)k_pages, (const T*)v_pages, block_table, token_request, positions, (T*)out,    \
+        n_tokens, n_head, n_kv_head, head_dim, v_dim, (const T*)gate, gate_stride, page_tokens, max_pages, window,      \
+        scale, num_pages, n_requests, slopes, key_block, softcap, sinks, v_stride)
+    if (is_bf16) {
+        if (v_dim <= 256) MG_LAUNCH_GENERIC(bf16, 8); else MG_LAUNCH_GENERIC(bf16, 16);
+    } else {
+        if (v_dim <= 256) MG_LAUNCH_GENERIC(float, 8); else MG_LAUNCH_GENERIC(float, 16);
+    }
+#undef MG_LAUNCH_GENERIC
     MG_CHECK_LAUNCH("paged_attention_generic");
     return MG_OK;
 }

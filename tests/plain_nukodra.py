@@ -63,16 +63,20 @@ def attention_mixer(h, w, p, m, eps):
     q = rms_norm(h @ w[p + "q"].T + w[p + "q.b"], w[p + "q.norm"], eps).view(T, heads, d)
     k = rms_norm(h @ w[p + "k"].T + w[p + "k.b"], w[p + "k.norm"], eps).view(T, groups, d)
     v = (h @ w[p + "v"].T + w[p + "v.b"]).view(T, groups, dv)
-    q = rotate(q, pos, m["rot"]["dims"], m["rot"]["base"])
-    k = rotate(k, pos, m["rot"]["dims"], m["rot"]["base"])
+    if m.get("rot") is not None:
+        q = rotate(q, pos, m["rot"]["dims"], m["rot"]["base"])
+        k = rotate(k, pos, m["rot"]["dims"], m["rot"]["base"])
     dist = pos[:, None] - pos[None, :]
-    seen = (dist >= 0) & (dist < m["mask"]["size"])
-    cap = m["softcap"]
+    seen = dist >= 0
+    if m.get("mask") is not None:
+        seen = seen & (dist < m["mask"]["size"])
+    cap = m.get("softcap")
     per = heads // groups
     out = torch.empty(T, heads, dv, dtype=h.dtype)
     for a in range(heads):
         s = (q[:, a] @ k[:, a // per].T) * m["scale"]
-        s = cap * torch.tanh(s / cap)
+        if cap is not None:
+            s = cap * torch.tanh(s / cap)
         s = s.masked_fill(~seen, -math.inf)
         sink = w[p + "sink"][a]
         top = torch.maximum(s.max(dim=-1, keepdim=True).values, sink)
@@ -159,12 +163,19 @@ def forward(cfg, w, tokens, dtype=torch.float64, return_layers=False):
     eps = cfg["norm"]["eps"]
     ids = torch.as_tensor(list(tokens), dtype=torch.long)
     x = w["embed"][ids]
-    X = x[None].repeat(cfg["streams"], 1, 1)
+    many = cfg.get("streams") is not None
+    X = x[None].repeat(cfg["streams"] if many else 1, 1, 1)
+    one = torch.ones(1, dtype=dtype)
+
+    def connection(name):
+        # without streams: u = x, x <- x + y
+        return (w[name + ".in"], w[name + ".mix"], w[name + ".out"]) if many else (one, one[None], one)
     latents = {}
     after = []
     for i, layer in enumerate(cfg["layers"]):
         p, m = f"l{i}.", layer["mixer"]
-        h = rms_norm(streams_read(X, w[p + "hc1.in"]), w[p + "norm1"], eps, 1.0)
+        a, M, b = connection(p + "hc1")
+        h = rms_norm(streams_read(X, a), w[p + "norm1"], eps, 1.0)
         if layer["type"] == "attention":
             y = attention_mixer(h, w, p + "mix.", m, eps)
         elif layer["type"] == "mamba2":
@@ -175,10 +186,20 @@ def forward(cfg, w, tokens, dtype=torch.float64, return_layers=False):
                 latents[i] = latent_of(h, w, p + "mix.", m, eps)
                 src = i
             y = latent_attention_mixer(h, w, p + "mix.", m, eps, latents[src])
-        X = streams_write(X, w[p + "hc1.mix"], w[p + "hc1.out"], y)
+        X = streams_write(X, M, b, y)
         if layer.get("mlp") is not None:
-            h = rms_norm(streams_read(X, w[p + "hc2.in"]), w[p + "norm2"], eps, 1.0)
-            X = streams_write(X, w[p + "hc2.mix"], w[p + "hc2.out"], dense_ff(h, w, p + "mlp."))
+            a, M, b = connection(p + "hc2")
+            h = rms_norm(streams_read(X, a), w[p + "norm2"], eps, 1.0)
+            X = streams_write(X, M, b, dense_ff(h, w, p + "mlp."))
         after.append(X.sum(0))
     logits = rms_norm(X.sum(0), w["final.norm"], eps, 1.0) @ w["embed"].T
     return (logits, after) if return_layers else logits
+
+
+def greedy(cfg, w, prompt, new_tokens, dtype=torch.float64):
+    """The prompt's greedy continuation, every token from a whole pass over the sequence so far."""
+    seq, out = list(prompt), []
+    for _ in range(new_tokens):
+        out.append(int(forward(cfg, w, seq, dtype)[-1].argmax()))
+        seq.append(out[-1])
+    return out

@@ -1,0 +1,284 @@
+"""Nukodra on the GPU against the plain implementation: the step function under every way of cutting
+requests into steps, batches, pages and slots used again, then generation through the entry point.  (The new
+mechanisms alone are in ``test_gpu_nukodra_parts.py``.)"""
+
+from __future__ import annotations
+
+import io
+import itertools
+import json
+
+import numpy as np
+import pytest
+import torch
+
+from nukodra_cases import (PAGE_TOKENS, assert_rows_close, config, plain_greedy, plain_logits, random_weights,
+                           relative_error, tokens_for)
+
+from mini_gpt_inference_b200 import EngineConfig, LLMEngine, NukodraConfig, SamplingParams
+from mini_gpt_inference_b200.engine.build import load_model, make_runner
+from mini_gpt_inference_b200.engine.runner import StepEntry
+
+pytestmark = pytest.mark.gpu
+
+# Largest |engine - plain| on a row of logits, over the row's own spread.  32-bit: rounding of sums.
+# bfloat16: both sides use the same weights; activations are rounded to 8 bits between kernels.  A
+# lost key, state, sink, stream or gate shows as 0.3 and more.
+TOL = {"float32": 3e-4, "bfloat16": 1e-1}
+CASES = [(w, d) for w in "ABCDEF" for d in ("float32", "bfloat16")]
+IDS = [f"{w}-{d}" for w, d in CASES]
+
+
+def setup(which, dtype, num_pages=64, seed=3, max_requests=4, raw=None):
+    from mini_gpt_inference_b200.kernels.ops import default_ops
+
+    raw = raw or config(which)
+    # (sharp softmaxes in 32-bit, where nothing but the order of sums differs; in bfloat16 they would magnify
+    # the rounding of queries and keys)
+    tensors = random_weights(raw, seed, sharp=3.0 if dtype == "float32" else 1.0, as_bfloat16=dtype == "bfloat16")
+    loaded = load_model(config=NukodraConfig.from_dict(raw), tensors=tensors, dtype=dtype, device="cuda:0")
+    runner = make_runner(loaded, default_ops("cuda:0"), PAGE_TOKENS[which], num_pages, max_requests)
+    return raw, tensors, runner, (TOL[dtype], 0.03 if dtype == "bfloat16" else 0.0)
+
+
+@pytest.mark.parametrize("which,dtype", CASES, ids=IDS)
+def test_whole_prompts(which, dtype):
+    raw, tensors, runner, tol = setup(which, dtype, num_pages=100)
+    pt = PAGE_TOKENS[which]
+    for length, seed in [(150, 1), (37, 2), (1, 3), (2, 4), (pt + 1, 5), (pt, 6), (190, 7)]:
+        tokens = tokens_for(raw, length, seed)
+        got = runner.step([StepEntry("r", tokens, list(range(length)))])
+        runner.finish("r")
+        assert got.shape == (length, raw["vocab"]) and got.dtype == torch.float32
+        assert_rows_close(got, plain_logits(raw, tensors, tokens), tol[0], f"whole prompt of {length}", outliers=tol[1])
+    runner.manager.check()
+    assert runner.manager.stats()["allocated_blocks"] == 0
+
+
+@pytest.mark.parametrize("which,dtype", CASES, ids=IDS)
+def test_prefill_then_single_tokens(which, dtype):
+    """A short prompt, then a long run of single tokens (replayed from a CUDA graph) that carries every window
+    over decoded tokens alone, and the same sequence token by token from the very first token."""
+    raw, tensors, runner, tol = setup(which, dtype)
+    tokens = tokens_for(raw, 150, 7)
+    want = plain_logits(raw, tensors, tokens)
+    outs = [runner.step([StepEntry("r", tokens[:9], list(range(9)))])]
+    outs += [runner.step([StepEntry("r", tokens[t: t + 1], [0])]) for t in range(9, 150)]
+    assert_rows_close(torch.cat(outs), want, tol[0], "prefill then single tokens", outliers=tol[1])
+    assert runner.graph_replays > 100
+    one_by_one = torch.cat([runner.step([StepEntry("s", tokens[t: t + 1], [0])]) for t in range(40)])
+    assert_rows_close(one_by_one, want[:40], tol[0], "single tokens from the first", outliers=tol[1])
+    if dtype == "float32":
+        # in 32-bit the cut into steps changes no bit
+        assert torch.equal(one_by_one, torch.cat(outs)[:40])
+
+
+@pytest.mark.parametrize("which,dtype", CASES, ids=IDS)
+def test_portions_of_changing_size(which, dtype):
+    raw, tensors, runner, tol = setup(which, dtype)
+    tokens = tokens_for(raw, 131, 8)
+    want = plain_logits(raw, tensors, tokens)
+    sizes = itertools.cycle([13, 7, 2, 5, 2, 1, 3, 16, 2, 9, 33])
+    outs, pos = [], 0
+    while pos < len(tokens):
+        n = min(next(sizes), len(tokens) - pos)
+        outs.append(runner.step([StepEntry("r", tokens[pos: pos + n], list(range(n)))]))
+        pos += n
+    assert_rows_close(torch.cat(outs), want, tol[0], "portions of changing size", outliers=tol[1])
+
+
+@pytest.mark.parametrize("which,dtype", CASES, ids=IDS)
+def test_mixed_batches_reuse_pages_and_slots(which, dtype):
+    """Up to four live requests, portions of some beside single tokens of others, requests left out of
+    steps; pages and state slots are handed out again.  Every cache row and state slot starts as NaN and
+    turns NaN again when its request ends."""
+    pt = PAGE_TOKENS[which]
+    lengths = [90, 29, 71, 3, 41, 2 * pt, 17, 55, 1]
+    pool = sum(sorted(-(-n // pt) for n in lengths)[-4:])
+    raw, tensors, runner, tol = setup(which, dtype, num_pages=pool)
+    for pages in runner.storage.k + runner.storage.v:
+        if pages is not None:
+            pages.fill_(float("nan"))
+    for state in runner.storage.state.values():
+        state.fill_(float("nan") if state.is_floating_point() else -1)
+    reqs = {f"q{i}": tokens_for(raw, n, 20 + i) for i, n in enumerate(lengths)}
+    want = {rid: plain_logits(raw, tensors, toks) for rid, toks in reqs.items()}
+    got = {rid: [] for rid in reqs}
+    waiting, live = list(reqs), {}
+    sizes = itertools.cycle([5, 1, 2, 11, 1, 1, 7, 3, 1, 2, 1, 1, 19])
+    gen = torch.Generator().manual_seed(99)
+    while waiting or live:
+        while waiting and len(live) < 4:
+            live[waiting.pop(0)] = 0
+        entries, order = [], []
+        for rid in list(live):
+            if len(live) > 1 and torch.rand((), generator=gen).item() < 0.25:
+                continue
+            pos = live[rid]
+            n = min(next(sizes), len(reqs[rid]) - pos)
+            entries.append(StepEntry(rid, reqs[rid][pos: pos + n], list(range(n))))
+            order.append((rid, n))
+            live[rid] = pos + n
+        if not entries:
+            continue
+        logits = runner.step(entries)
+        row = 0
+        for rid, n in order:
+            got[rid].append(logits[row: row + n].clone())
+            row += n
+            if live[rid] == len(reqs[rid]):
+                held = runner.manager.get(rid)
+                tables, slot = [list(t) for t in held.tables], held.state_slot
+                runner.finish(rid)
+                del live[rid]
+                for g, table in enumerate(tables):
+                    for page in table:
+                        if page >= 0:
+                            for pages in (runner.storage.k[g], runner.storage.v[g]):
+                                if pages is not None:
+                                    pages[:, page] = float("nan")
+                for state in runner.storage.state.values():
+                    state[slot] = float("nan") if state.is_floating_point() else -1
+    for rid in reqs:
+        assert_rows_close(torch.cat(got[rid]), want[rid], tol[0], f"request {rid} in mixed batches", outliers=tol[1])
+    runner.manager.check()
+    assert runner.manager.stats()["allocated_blocks"] == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_batch_of_unequal_requests_equals_each_alone(dtype):
+    raw, tensors, runner, tol = setup("A", dtype, num_pages=64, max_requests=8)
+    prompts = [tokens_for(raw, n, 70 + n) for n in (1, 2, 33, 64, 7)]
+    alone = []
+    for i, p in enumerate(prompts):
+        alone.append(runner.step([StepEntry(f"a{i}", p, list(range(len(p))))]))
+        runner.finish(f"a{i}")
+    together = runner.step([StepEntry(f"b{i}", p, list(range(len(p)))) for i, p in enumerate(prompts)])
+    if dtype == "float32":
+        assert torch.equal(together, torch.cat(alone))
+    else:
+        assert float(relative_error(together, torch.cat(alone).cpu()).max()) < tol[0]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_windows_pass_over_long_prompts_and_long_decoding(dtype):
+    """Sequences several windows long: the prompt's later tokens and every decoded token see only their
+    window's keys, while the latent layers and the state-space layer still carry the first tokens."""
+    raw, tensors, runner, tol = setup("B", dtype, num_pages=40)
+    tokens = tokens_for(raw, 400, 17)
+    want = plain_logits(raw, tensors, tokens)
+    outs = [runner.step([StepEntry("r", tokens[:300], list(range(300)))])]
+    outs += [runner.step([StepEntry("r", tokens[t: t + 1], [0])]) for t in range(300, 400)]
+    assert_rows_close(torch.cat(outs), want, tol[0], "long prompt, long decoding", outliers=tol[1])
+
+
+# ---- generation through the entry point, its scheduler and sampler ---------------------------------
+@pytest.mark.parametrize("which", "ABC")
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_engine(which, dtype):
+    raw = config(which)
+    tensors = random_weights(raw, 11, as_bfloat16=dtype == "bfloat16")
+    loaded = load_model(config=NukodraConfig.from_dict(raw), tensors=tensors, dtype=dtype, device="cuda:0")
+    engine = LLMEngine(loaded, EngineConfig(dtype=dtype, block_size=PAGE_TOKENS[which], num_blocks=48,
+                                            max_batch_size=3, max_num_batched_tokens=16, max_prefill_chunk=7))
+    prompts = [tokens_for(raw, n, 40 + i) for i, n in enumerate([5, 1, 23, 12, 2, 17])]
+    outs = engine.generate(prompts, SamplingParams(max_tokens=12, temperature=0.0))
+    for prompt, out in zip(prompts, outs):
+        assert len(out["token_ids"]) == 12 and out["finish_reason"] == "length"
+        seq = prompt + out["token_ids"]
+        want = plain_logits(raw, tensors, seq[:-1])
+        for i, token in enumerate(out["token_ids"]):
+            row = want[len(prompt) - 1 + i]
+            assert row.max() - row[token] <= 2 * TOL[dtype] * row.std(), (i, token, int(row.argmax()))
+        if dtype == "float32":
+            assert out["token_ids"] == plain_greedy(raw, tensors, prompt, 12)
+    assert engine.stats()["allocated_blocks"] == 0
+    engine.runner.manager.check()
+
+
+def test_preemption_and_recompute_through_the_engine():
+    """A pool too small for the three running requests (no window, so that no page comes back early): requests
+    are preempted, give back their pages and state slot, and are computed again from their first token in a
+    slot that another request used meanwhile."""
+    raw = config("C")
+    tensors = random_weights(raw, 14)
+    loaded = load_model(config=NukodraConfig.from_dict(raw), tensors=tensors, dtype="float32", device="cuda:0")
+    engine = LLMEngine(loaded, EngineConfig(dtype="float32", block_size=8, num_blocks=10, max_batch_size=3,
+                                            max_num_batched_tokens=16, max_prefill_chunk=7))
+    prompts = [tokens_for(raw, n, 60 + i) for i, n in enumerate([20, 25, 18, 9])]
+    outs = engine.generate(prompts, SamplingParams(max_tokens=16, temperature=0.0))
+    assert engine.scheduler.num_preemptions > 0
+    for prompt, out in zip(prompts, outs):
+        assert out["token_ids"] == plain_greedy(raw, tensors, prompt, 16)
+    assert engine.stats()["allocated_blocks"] == 0
+    engine.runner.manager.check()
+
+
+def test_long_decoding_through_the_engine():
+    raw = config("A")
+    tensors = random_weights(raw, 12)
+    loaded = load_model(config=NukodraConfig.from_dict(raw), tensors=tensors, dtype="float32", device="cuda:0")
+    engine = LLMEngine(loaded, EngineConfig(dtype="float32", block_size=8, num_blocks=40, max_batch_size=2))
+    prompt = tokens_for(raw, 3, 9)
+    out = engine.generate([prompt], SamplingParams(max_tokens=160, temperature=0.0))[0]
+    assert out["token_ids"] == plain_greedy(raw, tensors, prompt, 160)
+
+
+def test_trace_replay(tmp_path):
+    """The replay program on a model folder: two requests, portions beside single tokens, a slot and pages
+    used again by a third request."""
+    from mini_gpt_inference_b200.engine.trace import main
+    from mini_gpt_inference_b200.weights.safetensors_io import save_file
+
+    raw = config("A")
+    tensors = random_weights(raw, 13, as_bfloat16=True)
+    folder = tmp_path / "model"
+    folder.mkdir()
+    (folder / "config.json").write_text(json.dumps(raw))
+    save_file({k: v.to(torch.bfloat16) for k, v in tensors.items()}, folder / "model.safetensors")
+    a, b, c = tokens_for(raw, 50, 1), tokens_for(raw, 20, 2), tokens_for(raw, 64, 3)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:30], "want": [0, 29]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": a[30:31], "want": [0]}, {"id": "b", "tokens": b[:7], "want": []}], "end": []},
+        {"step": 2, "entries": [{"id": "b", "tokens": b[7:], "want": [12]}, {"id": "a", "tokens": a[31:], "want": [18]}], "end": ["a", "b"]},
+        {"step": 3, "entries": [{"id": "c", "tokens": c[:62], "want": [61]}], "end": []},
+        {"step": 4, "entries": [{"id": "c", "tokens": c[62:], "want": [0, 1]}], "end": ["c"]},
+    ]
+    for dtype in ("float32", "bfloat16"):
+        out = tmp_path / dtype
+        stdout = io.StringIO()
+        code = main(["--model", str(folder), "--dtype", dtype, "--out", str(out), "--max-tokens", "128",
+                     "--live-requests", "2"], stdin=io.StringIO("\n".join(json.dumps(s) for s in steps) + "\n"),
+                    stdout=stdout)
+        assert code == 0 and stdout.getvalue().split() == ["done", "0", "done", "1", "done", "2", "done", "3", "done", "4"]
+        la, lb, lc = (plain_logits(raw, tensors, t) for t in (a, b, c))
+        want = {0: la[[0, 29]], 1: la[[30]], 2: torch.stack([lb[19], la[49]]), 3: lc[[61]], 4: lc[[62, 63]]}
+        for step, rows in want.items():
+            got = torch.from_numpy(np.fromfile(out / f"{step}.f32", dtype="<f4").reshape(len(rows), raw["vocab"]))
+            assert_rows_close(got, rows, 2 * TOL[dtype], f"{dtype} step {step}")
+
+
+def test_command_line_writes_and_generates(tmp_path):
+    """bin/generate: a random-weights folder from a config.json, then greedy tokens from it that equal the
+    plain implementation's on the folder's own tensors."""
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    from mini_gpt_inference_b200.weights import load_file
+
+    root = Path(__file__).resolve().parent.parent
+    raw = config("D")
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(raw))
+    folder = tmp_path / "model"
+    made = subprocess.run([sys.executable, str(root / "bin" / "generate"), "--random-weights", "3", "--config", str(cfg_path),
+                           "--write-model", str(folder), "--weights-dtype", "bfloat16"], capture_output=True, text=True)
+    assert made.returncode == 0, made.stderr[-2000:]
+    prompt = tokens_for(raw, 9, 5)
+    run = subprocess.run([sys.executable, str(root / "bin" / "generate"), "--model", str(folder), "--dtype", "float32",
+                          "--prompt-ids", ",".join(map(str, prompt)), "--max-new-tokens", "8", "--temperature", "0"],
+                         capture_output=True, text=True)
+    assert run.returncode == 0, run.stderr[-2000:]
+    out = json.loads(run.stdout.strip().splitlines()[-1])
+    assert out["token_ids"] == plain_greedy(raw, load_file(folder / "model.safetensors"), prompt, 8)

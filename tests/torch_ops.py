@@ -69,7 +69,7 @@ class TorchOps:
             pages = table[r, keys // pt]
             assert (pages >= 0).all(), "attention reads a page that is not there"
             k = cache.k_pages[pages, :, keys % pt].float()      # [keys, Hkv, D]
-            v = cache.v_pages[pages, :, keys % pt].float()
+            v = k[..., :v_dim] if getattr(cache, "values_in_keys", False) else cache.v_pages[pages, :, keys % pt].float()
             for h in range(n_head):
                 kh = h // (n_head // n_kv_head)
                 s = (k[:, kh] @ q[i, h]) * scale
@@ -106,7 +106,7 @@ class TorchOps:
             cache.v_pages[page, :, off] = v[keep].to(cache.v_pages.dtype)
 
     def paged_attention_general(self, q, n_head, n_kv_head, head_dim, v_dim, scale, cache, ctx, gate=None,
-                                slopes=None, block=None):
+                                slopes=None, block=None, softcap=None, sinks=None):
         n = q.shape[0]
         qh = q[:, : n_head * head_dim].reshape(n, n_head, head_dim).float()
         out = torch.zeros(n, n_head, v_dim)
@@ -123,13 +123,20 @@ class TorchOps:
             pages = table[r, keys // pt]
             assert (pages >= 0).all(), "attention reads a page that is not there"
             k = cache.k_pages[pages, :, keys % pt].float()
-            v = cache.v_pages[pages, :, keys % pt].float()
+            v = k[..., :v_dim] if getattr(cache, "values_in_keys", False) else cache.v_pages[pages, :, keys % pt].float()
             for h in range(n_head):
                 kh = h // (n_head // n_kv_head)
                 scores = (k[:, kh] @ qh[i, h]) * scale
                 if slopes is not None:
                     scores = scores - slopes[h] * (p - keys).float()
-                out[i, h] = torch.softmax(scores, dim=0) @ v[:, kh]
+                if softcap:
+                    scores = softcap * torch.tanh(scores / softcap)
+                if sinks is not None:
+                    # one more term in the denominator, with no value: a key whose value is zero
+                    weights = torch.softmax(torch.cat([scores, sinks[h].float().view(1)]), dim=0)[:-1]
+                else:
+                    weights = torch.softmax(scores, dim=0)
+                out[i, h] = weights @ v[:, kh]
         out = out.reshape(n, n_head * v_dim)
         if gate is not None:
             out = out * torch.sigmoid(gate.float())
@@ -216,8 +223,12 @@ class TorchOps:
     def concat_cast(self, a32, b32, out_dtype):
         return torch.cat([a32, b32], dim=-1).to(out_dtype)
 
-    def matrix_memory_scan(self, ctx, mode, proj, q_off, k_off, v_off, n_head, head_dim, v_dim, gates, constant, state):
+    def matrix_memory_scan(self, ctx, mode, proj, q_off, k_off, v_off, n_head, head_dim, v_dim, gates, constant, state,
+                           state_offset=0, qk_group=1, head_consts=None):
         n = proj.shape[0]
+        if mode == "ssd":
+            return self._state_space_scan(ctx, proj, q_off, k_off, v_off, n_head, head_dim, v_dim, gates, state,
+                                          state_offset, qk_group, head_consts), None
         q = proj[:, q_off: q_off + n_head * head_dim].float().reshape(n, n_head, head_dim) * head_dim ** -0.5
         k = proj[:, k_off: k_off + n_head * head_dim].float().reshape(n, n_head, head_dim)
         v = proj[:, v_off: v_off + n_head * v_dim].float().reshape(n, n_head, v_dim)
@@ -258,6 +269,30 @@ class TorchOps:
                 flat[n_head * cols * head_dim:] = m
         return out.reshape(n, n_head * v_dim), aux
 
+    def _state_space_scan(self, ctx, proj, q_off, k_off, v_off, n_head, n_state, v_dim, steps, state, state_offset,
+                          qk_group, head_consts):
+        n, groups = proj.shape[0], n_head // qk_group
+        c = proj[:, q_off: q_off + groups * n_state].float().reshape(n, groups, n_state).repeat_interleave(qk_group, 1)
+        b = proj[:, k_off: k_off + groups * n_state].float().reshape(n, groups, n_state).repeat_interleave(qk_group, 1)
+        x = proj[:, v_off: v_off + n_head * v_dim].float().reshape(n, n_head, v_dim)
+        a, d = head_consts[:n_head], head_consts[n_head:]
+        out = torch.zeros(n, n_head, v_dim)
+        size = n_head * v_dim * n_state
+        for r in range(ctx.num_requests):
+            start, count = int(ctx.req_q_start[r]), int(ctx.req_q_len[r])
+            if count == 0:
+                continue
+            flat = state[int(ctx.req_state_slot[r])]
+            S = flat[state_offset: state_offset + size].view(n_head, v_dim, n_state).clone()
+            if int(ctx.req_ctx_before[r]) == 0:
+                S.zero_()
+            for i in range(start, start + count):
+                dt = torch.nn.functional.softplus(steps[i].float(), threshold=1e9)
+                S = torch.exp(-torch.exp(a) * dt)[:, None, None] * S + dt[:, None, None] * x[i][:, :, None] * b[i][:, None, :]
+                out[i] = torch.einsum("hvn,hn->hv", S, c[i]) + d[:, None] * x[i]
+            flat[state_offset: state_offset + size] = S.reshape(-1)
+        return out.reshape(n, n_head * v_dim)
+
     def head_norm_gate(self, out32, aux, gate, gain, n_head, v_dim, eps, per_head_gain, gate_activation, out_dtype,
                        positions=None):
         n = out32.shape[0]
@@ -285,3 +320,120 @@ class TorchOps:
             return ids
         out.copy_(ids)
         return out
+
+    # ---- what the fourth architecture adds -----------------------------------------------------------
+    def streams_spread(self, x32, streams):
+        return x32[None].repeat(int(streams), 1, 1)
+
+    def streams_read(self, streams32, weights, want_zeros=False):
+        u = torch.einsum("s,stc->tc", weights.float(), streams32)
+        return (u, torch.zeros_like(u)) if want_zeros else u
+
+    def streams_sum(self, streams32):
+        return streams32.sum(0)
+
+    def streams_write(self, streams32, mix, weights, y32, next_read=None):
+        new = torch.einsum("sr,stc->rtc", mix.float(), streams32) + weights.float()[:, None, None] * y32[None]
+        streams32.copy_(new)
+        return self.streams_read(streams32, next_read, want_zeros=True) if next_read is not None else None
+
+    @staticmethod
+    def _turn(x, positions, rot_dims, freq):
+        """x: [tokens, heads, features]; the first rot_dims features of each head by position * freq."""
+        if not rot_dims:
+            return x
+        half = rot_dims // 2
+        angle = positions.clamp(min=0).float()[:, None] * freq.float()[None, :]
+        cos, sin = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
+        u, v = x[..., :half], x[..., half:rot_dims]
+        return torch.cat([u * cos - v * sin, v * cos + u * sin, x[..., rot_dims:]], dim=-1)
+
+    def qk_norm_rotary(self, proj, n_head, n_kv_head, head_dim, v_dim, q_off, k_off, v_off, norm, eps, rot_dims, freq,
+                       cache, slots, positions, q_gain=None, k_gain=None):
+        n = proj.shape[0]
+        live = positions >= 0
+
+        def whole(x, gain):
+            return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * gain if norm else x
+
+        q = whole(proj[:, q_off: q_off + n_head * head_dim].float(), q_gain).reshape(n, n_head, head_dim)
+        k = whole(proj[:, k_off: k_off + n_kv_head * head_dim].float(), k_gain).reshape(n, n_kv_head, head_dim)
+        q, k = self._turn(q, positions, rot_dims, freq), self._turn(k, positions, rot_dims, freq)
+        v = proj[:, v_off: v_off + n_kv_head * v_dim].float().reshape(n, n_kv_head, v_dim)
+        proj[live, q_off: q_off + n_head * head_dim] = q[live].reshape(int(live.sum()), -1).to(proj.dtype)
+        if cache is not None and cache.writes:
+            keep = live & (slots >= 0)
+            page, off = slots[keep].long() // cache.page_tokens, slots[keep].long() % cache.page_tokens
+            cache.k_pages[page, :, off] = k[keep].to(cache.k_pages.dtype)
+            cache.v_pages[page, :, off] = v[keep].to(cache.v_pages.dtype)
+
+    def latent_prepare(self, proj, n_head, q_off, q_dim, rot_dim, low_off, rank, gain, eps, freq, cache, slots, positions):
+        n = proj.shape[0]
+        q_in = proj[:, q_off: q_off + n_head * (q_dim + rot_dim)].float().reshape(n, n_head, q_dim + rot_dim)
+        q = torch.zeros(n, n_head, rank + rot_dim)
+        q[..., rank:] = self._turn(q_in[..., q_dim:], positions, rot_dim, freq)
+        if cache is not None and cache.writes:
+            c = proj[:, low_off: low_off + rank].float()
+            c = c / torch.sqrt((c * c).mean(-1, keepdim=True) + eps) * gain
+            shared = self._turn(proj[:, None, low_off + rank: low_off + rank + rot_dim].float(), positions, rot_dim, freq)[:, 0]
+            keep = (positions >= 0) & (slots >= 0)
+            page, off = slots[keep].long() // cache.page_tokens, slots[keep].long() % cache.page_tokens
+            cache.k_pages[page, 0, off] = torch.cat([c, shared], dim=-1)[keep].to(cache.k_pages.dtype)
+        return q.reshape(n, -1).to(proj.dtype)
+
+    def head_linear(self, x, x_off, x_head, weight, rows_are_inputs, n_head, n_in, n_out, gate=None, out=None, out_off=0,
+                    out_head=None):
+        n = x.shape[0]
+        cols = x_off + x_head * torch.arange(n_head)[:, None] + torch.arange(n_in)[None, :]
+        xs = x[:, cols.reshape(-1)].float().reshape(n, n_head, n_in)
+        w = weight.float().reshape(n_head, n_in, n_out) if rows_are_inputs else weight.float().reshape(n_head, n_out, n_in).transpose(1, 2)
+        y = torch.einsum("nhi,hio->nho", xs, w)
+        if gate is not None:
+            y = y * torch.sigmoid(gate.float().reshape(n, n_head, n_out))
+        if out is None:
+            return y.reshape(n, n_head * n_out).to(x.dtype)
+        out_head = n_out if out_head is None else out_head
+        where = out_off + out_head * torch.arange(n_head)[:, None] + torch.arange(n_out)[None, :]
+        out[:, where.reshape(-1)] = y.reshape(n, -1).to(out.dtype)
+        return out
+
+    def causal_conv_silu(self, ctx, x, x_off, channels, taps, bias, state):
+        n, width = x.shape[0], taps.shape[1]
+        out = torch.zeros(n, channels)
+        for r in range(ctx.num_requests):
+            start, count = int(ctx.req_q_start[r]), int(ctx.req_q_len[r])
+            if count == 0:
+                continue
+            before = state[int(ctx.req_state_slot[r]), : (width - 1) * channels].view(width - 1, channels).clone()
+            if int(ctx.req_ctx_before[r]) == 0:
+                before.zero_()
+            elif int(ctx.req_ctx_before[r]) < width - 1:       # rows before the sequence's start are zeros
+                before[: width - 1 - int(ctx.req_ctx_before[r])] = 0
+            rows = torch.cat([before, x[start: start + count, x_off: x_off + channels].float()], dim=0)
+            y = bias.float()[None, :].repeat(count, 1) if bias is not None else torch.zeros(count, channels)
+            for j in range(width):
+                y = y + rows[j: j + count] * taps[:, j].float()[None, :]
+            out[start: start + count] = y * torch.sigmoid(y)
+        return out.to(x.dtype)
+
+    def conv_state_update(self, ctx, x, x_off, channels, n_taps, state):
+        keep = n_taps - 1
+        if keep <= 0:
+            return
+        for r in range(ctx.num_requests):
+            start, count = int(ctx.req_q_start[r]), int(ctx.req_q_len[r])
+            if count == 0:
+                continue
+            slot = int(ctx.req_state_slot[r])
+            before = state[slot, : keep * channels].view(keep, channels).clone()
+            if int(ctx.req_ctx_before[r]) == 0:
+                before.zero_()
+            rows = torch.cat([before, x[start: start + count, x_off: x_off + channels].float()], dim=0)
+            state[slot, : keep * channels] = rows[-keep:].reshape(-1)
+
+    def gated_group_norm(self, out32, gate, gain, parts, eps, out_dtype, positions=None):
+        n, width = out32.shape
+        g = gate.float()
+        y = (out32 * g * torch.sigmoid(g)).view(n, parts, width // parts)
+        y = y / torch.sqrt((y * y).mean(-1, keepdim=True) + eps)
+        return (y.reshape(n, width) * gain).to(out_dtype)
