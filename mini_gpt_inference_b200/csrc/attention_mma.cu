@@ -18,6 +18,11 @@
 //          (token, key/value head) last merges the ranges, applies the gate and stores (or a second
 //          kernel does, if no counters are given).
 //
+// Further, all parameters: `softcap` (a score s, scale included, becomes softcap * tanh(s / softcap)), `sinks`
+// (one learned number per head whose exponential joins the softmax's denominator, with no key and no value: it is
+// added where a row's sum is final, in the tiles' epilogue and in the merge of the ranges), and `v_stride` (a
+// token's values are the first dv features of a wider row, its key row for instance).
+//
 // Keys are always read from the pages, whichever step wrote them.  Rows of pages beyond a request's
 // last key are never multiplied into a result (their values are replaced by zeros in shared memory).
 #include <math.h>
@@ -54,7 +59,15 @@ struct AttnParams {
     float scale_log2;             // scale * log2(e)
     const float* slopes;          // [H] or null: slope_h * (i - j) is taken off the score of query i and key j
     int block;                    // > 0: a query sees only the keys of its own block of this many positions
+    float cap_log2;               // > 0: softcap * log2(e)
+    const float* sinks;           // [H] or null
+    int v_stride;                 // elements between the value rows of neighbouring tokens
 };
+
+// What a head's sink adds to a row's sum that is held relative to the maximum m (in powers of two).
+__device__ __forceinline__ float sink_term(const AttnParams& p, int head, float m) {
+    return p.sinks ? exp2f(p.sinks[head] * LOG2E - m) : 0.f;
+}
 
 // The first key that a query at `pos` sees: the window's, raised to the first position of the query's block.
 __device__ __forceinline__ int first_visible(const AttnParams& p, int pos) {
@@ -117,7 +130,7 @@ __device__ __forceinline__ void load_block(const AttnParams& p, const int* table
             row = ((size_t)page * p.n_kv_head + kv_head) * p.page_tokens + within;
         }
         if (c < kc) cp_async16(ks + key * (DP + PAD) + c * 8, p.k_pages + row * p.d + c * 8, real);
-        else cp_async16(vs + key * (DVP + PAD) + (c - kc) * 8, p.v_pages + row * p.dv + (c - kc) * 8, real);
+        else cp_async16(vs + key * (DVP + PAD) + (c - kc) * 8, p.v_pages + row * p.v_stride + (c - kc) * 8, real);
     }
 }
 
@@ -152,7 +165,7 @@ template <int DP, int DVP, int NT>
 __device__ __forceinline__ void attend(const uint32_t (&qf)[DP / 16][4], const bf16* ks, const bf16* vs, int k_first,
                                        int j_first, const int (&pos)[2], const int (&lo)[2], bool all_visible,
                                        float scale_log2, float (&m)[2], float (&l)[2], float (&o)[DVP / 8][4], int lane,
-                                       const float (&slope_log2)[2], bool biased) {
+                                       const float (&slope_log2)[2], bool biased, float cap_log2) {
     float s[NT][4];
 #pragma unroll
     for (int n = 0; n < NT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
@@ -183,8 +196,9 @@ __device__ __forceinline__ void attend(const uint32_t (&qf)[DP / 16][4], const b
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int j = j_first + n * 8 + 2 * (lane & 3) + (e & 1), r = e >> 1;
-                const float v = (j <= pos[r] && j >= lo[r]) ? fmaf(s[n][e], scale_log2, -slope_log2[r] * (float)(pos[r] - j))
-                                                            : -INFINITY;
+                float sc = s[n][e] * scale_log2;
+                if (cap_log2 > 0.f) sc = cap_log2 * tanhf(sc / cap_log2);
+                const float v = (j <= pos[r] && j >= lo[r]) ? sc - slope_log2[r] * (float)(pos[r] - j) : -INFINITY;
                 s[n][e] = v;
                 bm[r] = fmaxf(bm[r], v);
             }
@@ -295,8 +309,8 @@ attention_tiles_kernel(const AttnParams p) {
         lo[r] = pos[r] >= 0 ? first_visible(p, pos[r]) : 0;
         qrow[r] = live ? p.q + (size_t)token[r] * p.q_stride + (size_t)head[r] * p.d : nullptr;
     }
-    const bool biased = p.slopes != nullptr;
-    const float slope_log2[2] = {biased ? p.slopes[head[0]] * LOG2E : 0.f, biased ? p.slopes[head[1]] * LOG2E : 0.f};
+    const bool biased = p.slopes != nullptr || p.cap_log2 > 0.f;
+    const float slope_log2[2] = {p.slopes ? p.slopes[head[0]] * LOG2E : 0.f, p.slopes ? p.slopes[head[1]] * LOG2E : 0.f};
     uint32_t qf[DP / 16][4];
     load_q<DP>(qf, qrow[0], qrow[1], p.d, lane);
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f}, o[DVP / 8][4];
@@ -328,12 +342,13 @@ attention_tiles_kernel(const AttnParams p) {
         if (j0 <= warp_hi)
             attend<DP, DVP, 8>(qf, ks + buf * STAGE, vs + buf * STAGE, 0, j0, pos, lo,
                                j0 + KB - 1 <= warp_first_pos && j0 >= warp_max_lo, p.scale_log2, m, l, o, lane, slope_log2,
-                               biased);
+                               biased, p.cap_log2);
         __syncthreads();                                    // the buffer is free for the block after the next
     }
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         if (pos[r] < 0) continue;
+        l[r] += sink_term(p, head[r], m[r]);
         const float inv = l[r] > 0.f ? 1.0f / l[r] : 0.f;
         bf16* orow = p.out + (size_t)token[r] * p.n_head * p.dv + (size_t)head[r] * p.dv;
         const bf16* grow = p.gate ? p.gate + (size_t)token[r] * p.gate_stride + (size_t)head[r] * p.dv : nullptr;
@@ -400,9 +415,9 @@ attention_split_kernel(const AttnParams p) {
             lo[r] = lo_row;
             qrow[r] = has_row ? p.q + (size_t)token * p.q_stride + (size_t)(kv_head * group + row) * p.d : nullptr;
         }
-        const bool biased = p.slopes != nullptr;
-        const float slope_log2[2] = {biased && row0 < group ? p.slopes[kv_head * group + row0] * LOG2E : 0.f,
-                                     biased && row0 + 8 < group ? p.slopes[kv_head * group + row0 + 8] * LOG2E : 0.f};
+        const bool biased = p.slopes != nullptr || p.cap_log2 > 0.f;
+        const float slope_log2[2] = {p.slopes && row0 < group ? p.slopes[kv_head * group + row0] * LOG2E : 0.f,
+                                     p.slopes && row0 + 8 < group ? p.slopes[kv_head * group + row0 + 8] * LOG2E : 0.f};
         uint32_t qf[DP / 16][4];
         load_q<DP>(qf, qrow[0], qrow[1], p.d, lane);
         const int page_shift = (p.page_tokens & (p.page_tokens - 1)) == 0 ? __ffs(p.page_tokens) - 1 : -1;
@@ -421,7 +436,7 @@ attention_split_kernel(const AttnParams p) {
             __syncthreads();
             if (j0 + warp * 16 <= last)
                 attend<DP, DVP, 2>(qf, ks + buf * STAGE, vs + buf * STAGE, warp * 16, j0 + warp * 16, pos, lo, false,
-                                   p.scale_log2, m, l, o, lane, slope_log2, biased);
+                                   p.scale_log2, m, l, o, lane, slope_log2, biased, p.cap_log2);
             __syncthreads();
         }
     }
@@ -491,6 +506,7 @@ attention_split_kernel(const AttnParams p) {
             sum += f * __ldcg(p.part_ml + (base + sp) * 2 + 1);
             acc += f * __ldcg(p.part_o + (base + sp) * p.dv + c);
         }
+        sum += sink_term(p, head, mm);
         acc = sum > 0.f ? acc / sum : 0.f;
         if (p.gate) acc *= logistic(__bfloat162float(p.gate[(size_t)token * p.gate_stride + (size_t)head * p.dv + c]));
         p.out[(size_t)token * p.n_head * p.dv + (size_t)head * p.dv + c] = __float2bfloat16_rn(acc);
@@ -530,7 +546,7 @@ __global__ void attention_merge_kernel(const AttnParams p) {
             weight[s] = w;
             sum += w * p.part_ml[(base + s) * 2 + 1];
         }
-        sum = warp_sum(sum);
+        sum = warp_sum(sum) + sink_term(p, head, mm);
         if (threadIdx.x == 0) norm = sum > 0.f ? 1.0f / sum : 0.f;
     }
     __syncthreads();
@@ -587,18 +603,23 @@ MG_API long long mg_attention_mma_scratch_floats(int n_tokens, int n_head, int d
 // single_tokens = 1: every token is alone in its request's step (splits ranges of split_keys keys,
 // scratch of mg_attention_mma_scratch_floats floats; counters: n_tokens * n_kv_head zeros that are left
 // as zeros, or null to merge the ranges in a second kernel); 0: n_tiles tiles of tile_tokens tokens, found
-// from req_q_start / req_q_len.  slopes: [n_head] 32-bit or null; key_block <= 0: no block mask.  Returns MG_ERR_UNSUPPORTED for sizes it does not take.
+// from req_q_start / req_q_len.  slopes: [n_head] 32-bit or null; key_block <= 0: no block mask; softcap <= 0: none;
+// sinks: [n_head] 32-bit or null; v_stride: elements between value rows (0: dv).  Returns MG_ERR_UNSUPPORTED for sizes
+// it does not take.
 MG_API int mg_attention_mma(const void* q, int q_stride, const void* k_pages, const void* v_pages, const int* block_table,
                             const int* token_request, const int* positions, const int* req_q_start,
                             const int* req_q_len, const void* gate, int gate_stride, void* out, float* scratch,
                             int* counters, int n_tokens, int n_requests, int n_head, int n_kv_head, int d, int dv, int page_tokens,
                             int max_pages, int window, float scale, int num_pages, int single_tokens, int n_tiles,
-                            int tile_tokens, int splits, int split_keys, const float* slopes, int key_block, void* stream) {
+                            int tile_tokens, int splits, int split_keys, const float* slopes, int key_block, float softcap,
+                            const float* sinks, int v_stride, void* stream) {
     if (n_tokens == 0) return MG_OK;
     MG_REQUIRE(n_tokens > 0 && n_head > 0 && n_kv_head > 0 && n_head % n_kv_head == 0 && page_tokens > 0 && max_pages > 0,
                "attention: bad sizes");
     const int group = n_head / n_kv_head;
-    const bool aligned = d % 8 == 0 && dv % 8 == 0 && q_stride % 8 == 0 && (gate == nullptr || gate_stride % 2 == 0) &&
+    if (v_stride <= 0) v_stride = dv;
+    MG_REQUIRE(v_stride >= dv, "attention: value rows shorter than the values");
+    const bool aligned = d % 8 == 0 && dv % 8 == 0 && v_stride % 8 == 0 && q_stride % 8 == 0 && (gate == nullptr || gate_stride % 2 == 0) &&
                          ((uintptr_t)q % 16 == 0) && ((uintptr_t)k_pages % 16 == 0) && ((uintptr_t)v_pages % 16 == 0) &&
                          ((uintptr_t)out % 4 == 0) && ((uintptr_t)gate % 4 == 0);
     if (!aligned || d > 128 || dv > 128 || group > (single_tokens ? 16 : 64) || n_kv_head > 65535) return MG_ERR_UNSUPPORTED;
@@ -611,6 +632,7 @@ MG_API int mg_attention_mma(const void* q, int q_stride, const void* k_pages, co
     p.page_tokens = page_tokens; p.max_pages = max_pages; p.window = window > 0 ? window : 0; p.num_pages = num_pages;
     p.tile_tokens = tile_tokens; p.splits = splits; p.split_keys = split_keys; p.scale_log2 = scale * LOG2E;
     p.slopes = slopes; p.block = key_block > 0 ? key_block : 0;
+    p.cap_log2 = softcap > 0.f ? softcap * LOG2E : 0.f; p.sinks = sinks; p.v_stride = v_stride;
     if (single_tokens) {
         MG_REQUIRE(scratch != nullptr && splits > 0 && splits <= 65535 && split_keys > 0 && split_keys % KB == 0,
                    "attention: the ranges of keys want scratch and sizes that are multiples of %d", KB);

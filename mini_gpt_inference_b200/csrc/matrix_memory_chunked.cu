@@ -19,6 +19,12 @@
 // a chunk's U is held relative to its own maximum and rescaled in kernel 2), and the normaliser is the
 // value column "1": n_t . q_t is that column's output and goes to `aux` with m_t, as in the sequential scan.
 // All sums, decays, exponentials and the state are 32-bit; only q, k and v arrive in the compute type.
+//
+// State-space duality (Mamba-2) runs through the kernels of gated linear attention: its decay exp(-exp(A_h) dt_t)
+// is one number per head and token, which is a decay per key channel that happens to be the same in all of
+// them.  What differs is read where the rows are loaded (`ssd`): the logarithm of the decay is -exp(A_h) dt_t with
+// dt_t = softplus(gates[t, h]), the values enter the memory as dt_t x_t, queries are not scaled, q and k (the C and
+// B of the state-space form) are shared by `qk_group` neighbouring heads, and D_h x_t is added to the output.
 #include <math.h>
 
 #include "common.cuh"
@@ -32,6 +38,7 @@ constexpr int SCAN_THREADS = 256;   // kernel 2
 constexpr int SCAN_AHEAD = 8;       // chunks whose loads are in flight at once in kernel 2
 
 __device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+__device__ __forceinline__ float softplus(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
 
 struct ChunkParams {
     const void* proj; int ld, q_off, k_off, v_off;
@@ -46,6 +53,8 @@ struct ChunkParams {
     float* out; float* aux;
     int n_chunks, n_requests, n_tokens, n_head, d, dv, L, n_slots;
     float constant;
+    int ssd, qk_group;            // the state-space form: q and k columns of head h / qk_group
+    const float* head_consts;     // ssd: [2 H]: A_h, then D_h
 };
 
 // ---- kernel 1 ----------------------------------------------------------------------------------------
@@ -66,10 +75,15 @@ __global__ void __launch_bounds__(THREADS) chunk_local_kernel(const ChunkParams 
     if (!MLSTM) {
         // the logarithms of the decays, all at once; then their running sums, a thread per key channel; then the
         // keys as the chunk's end sees them, all at once again
-        const float inv_tau = 1.0f / p.constant;
+        const float inv_tau = p.ssd ? 0.f : 1.0f / p.constant;
+        const float rate = p.ssd ? expf(p.head_consts[h]) : 0.f;
         for (int idx = tid; idx < L * D; idx += THREADS) {
             const int j = idx / D, d = idx - j * D;
-            fc[j * (D + 1) + d] = j < count ? log_sigmoid(p.gates[(size_t)(row0 + j) * p.gates_ld + (size_t)h * D + d]) * inv_tau : 0.f;
+            float la = 0.f;
+            if (j < count)
+                la = p.ssd ? -rate * softplus(p.gates[(size_t)(row0 + j) * p.gates_ld + h])
+                           : log_sigmoid(p.gates[(size_t)(row0 + j) * p.gates_ld + (size_t)h * D + d]) * inv_tau;
+            fc[j * (D + 1) + d] = la;
         }
         __syncthreads();
         for (int d = tid; d < D; d += THREADS) {
@@ -86,7 +100,7 @@ __global__ void __launch_bounds__(THREADS) chunk_local_kernel(const ChunkParams 
             float kv = 0.f;
             if (j < count) {
                 p.cum[((size_t)(row0 + j) * p.n_head + h) * D + d] = b;
-                kv = to_float(proj[(size_t)(row0 + j) * p.ld + p.k_off + (size_t)h * D + d]) * expf(b_end - b);
+                kv = to_float(proj[(size_t)(row0 + j) * p.ld + p.k_off + (size_t)(h / p.qk_group) * D + d]) * expf(b_end - b);
             }
             kt[j * (D + 1) + d] = kv;
         }
@@ -134,6 +148,7 @@ __global__ void __launch_bounds__(THREADS) chunk_local_kernel(const ChunkParams 
         if (j < count) {
             if (e < p.dv) vv = to_float(proj[(size_t)(row0 + j) * p.ld + p.v_off + (size_t)h * p.dv + e]);
             else if (MLSTM && e == p.dv) vv = 1.f;
+            if (!MLSTM && p.ssd) vv *= softplus(p.gates[(size_t)(row0 + j) * p.gates_ld + h]);
         }
         vs[idx] = vv;
     }
@@ -225,12 +240,14 @@ __global__ void __launch_bounds__(THREADS) chunk_output_kernel(const ChunkParams
     const int row0 = p.chunks[4 * c + 1], count = p.chunks[4 * c + 2];
     if (!MG_GUARDED(matrix_memory_chunked, MG_GUARD_ROW, row0 + count - 1, p.n_tokens) || count <= 0 || count > L) return;
     const T* proj = reinterpret_cast<const T*>(p.proj);
-    const float q_scale = 1.0f / sqrtf((float)D);
+    const bool ssd = !MLSTM && p.ssd;
+    const float q_scale = ssd ? 1.0f : 1.0f / sqrtf((float)D);
+    const int hq = h / p.qk_group;
     for (int idx = tid; idx < L * D; idx += THREADS) {
         const int j = idx / D, d = idx - j * D;
         float qv = 0.f, kv = 0.f, bv = 0.f;
         if (j < count) {
-            const T* row = proj + (size_t)(row0 + j) * p.ld + (size_t)h * D + d;
+            const T* row = proj + (size_t)(row0 + j) * p.ld + (size_t)hq * D + d;
             qv = to_float(row[p.q_off]) * q_scale;
             kv = to_float(row[p.k_off]);
             if (!MLSTM) bv = p.cum[((size_t)(row0 + j) * p.n_head + h) * D + d];
@@ -241,7 +258,9 @@ __global__ void __launch_bounds__(THREADS) chunk_output_kernel(const ChunkParams
     }
     for (int idx = tid; idx < L * Dv; idx += THREADS) {
         const int j = idx / Dv, e = idx - j * Dv;
-        vs[idx] = j < count ? to_float(proj[(size_t)(row0 + j) * p.ld + p.v_off + (size_t)h * Dv + e]) : 0.f;
+        float vv = j < count ? to_float(proj[(size_t)(row0 + j) * p.ld + p.v_off + (size_t)h * Dv + e]) : 0.f;
+        if (ssd && j < count) vv *= softplus(p.gates[(size_t)(row0 + j) * p.gates_ld + h]);
+        vs[idx] = vv;
     }
     const float* S_prev = p.chunk_state + ((size_t)c * p.n_head + h) * DvE * D;
     for (int idx = tid; idx < DvE * D; idx += THREADS) {
@@ -335,8 +354,13 @@ __global__ void __launch_bounds__(THREADS) chunk_output_kernel(const ChunkParams
         for (int u = 0; u < 4; ++u)
 #pragma unroll
             for (int x = 0; x < 4; ++x)
-                if (t0 + u < count && e0 + 32 * x < Dv)
-                    p.out[((size_t)(row0 + t0 + u) * p.n_head + h) * Dv + e0 + 32 * x] = acc[u][x];
+                if (t0 + u < count && e0 + 32 * x < Dv) {
+                    float o = acc[u][x];
+                    if (ssd)                                          // D_h x_t, with x_t as it arrived
+                        o = fmaf(p.head_consts[p.n_head + h],
+                                 to_float(proj[(size_t)(row0 + t0 + u) * p.ld + p.v_off + (size_t)h * Dv + e0 + 32 * x]), o);
+                    p.out[((size_t)(row0 + t0 + u) * p.n_head + h) * Dv + e0 + 32 * x] = o;
+                }
     }
     if (MLSTM && tid < count) {                                       // the normaliser's column, a row a thread
         const int t = tid;
@@ -390,22 +414,29 @@ MG_API int mg_matrix_memory_chunk_tokens(int head_dim, int v_dim, int mlstm) {
 // chunks: [n_chunks, 4] (request, first row, tokens <= chunk_tokens, unused) in row order; req_chunks:
 // [n_requests, 2] (first chunk, chunks); cum: [n_tokens, n_head, mlstm ? 2 : head_dim] floats; chunk_state:
 // [n_chunks, n_head, v_dim + mlstm, head_dim] floats; chunk_meta: [n_chunks, n_head, 4] floats (mlstm; else null).
+// qk_group > 0 with head_consts ([A_0 .. A_(H-1), D_0 .. D_(H-1)], 32-bit): the state-space form (not with mlstm);
+// gates then hold one step size per head before its softplus, and `state` points at the memories of slot 0.
 MG_API int mg_matrix_memory_chunked(const void* proj, int ld, int q_off, int k_off, int v_off, const float* gates,
                                     int gates_ld, const int* chunks, const int* req_chunks, const int* req_ctx_before,
                                     const int* req_state_slot, float* state, long long state_stride, float* cum,
                                     float* chunk_state, float* chunk_meta, float* out, float* aux, int n_chunks,
                                     int chunk_tokens, int n_requests, int n_tokens, int n_head, int head_dim, int v_dim,
-                                    float constant, int mlstm, int n_slots, int is_bf16, void* stream) {
+                                    float constant, int mlstm, int n_slots, int is_bf16, int qk_group,
+                                    const float* head_consts, void* stream) {
     if (n_requests == 0 || n_tokens == 0 || n_chunks == 0) return MG_OK;
     MG_REQUIRE(n_requests > 0 && n_tokens > 0 && n_chunks > 0 && n_head > 0 && head_dim > 0 && v_dim > 0 && n_slots > 0,
                "matrix memory (chunks): bad sizes");
     MG_REQUIRE(n_head <= 65535 && n_requests <= 65535, "matrix memory (chunks): too many heads or requests");
-    MG_REQUIRE(constant > 0.f, "matrix memory (chunks): tau and the gates' cap must be positive");
+    const bool ssd = head_consts != nullptr;
+    MG_REQUIRE(ssd || constant > 0.f, "matrix memory (chunks): tau and the gates' cap must be positive");
+    MG_REQUIRE(!ssd || (!mlstm && qk_group > 0 && n_head % qk_group == 0), "matrix memory (chunks): %d heads do not form groups of %d", n_head, qk_group);
+    if (!ssd) qk_group = 1;
+    const int qk_heads = n_head / qk_group;
     const int cols = v_dim + (mlstm ? 1 : 0);
     MG_REQUIRE(state_stride >= (long long)n_head * cols * head_dim + (mlstm ? n_head : 0), "matrix memory (chunks): the state slots are too small");
-    MG_REQUIRE(q_off >= 0 && k_off >= 0 && v_off >= 0 && q_off + n_head * head_dim <= ld && k_off + n_head * head_dim <= ld &&
+    MG_REQUIRE(q_off >= 0 && k_off >= 0 && v_off >= 0 && q_off + qk_heads * head_dim <= ld && k_off + qk_heads * head_dim <= ld &&
                    v_off + n_head * v_dim <= ld, "matrix memory (chunks): heads outside the rows");
-    MG_REQUIRE(gates_ld >= (mlstm ? 2 * n_head : n_head * head_dim), "matrix memory (chunks): the gates' rows are too short");
+    MG_REQUIRE(gates_ld >= (mlstm ? 2 * n_head : ssd ? n_head : n_head * head_dim), "matrix memory (chunks): the gates' rows are too short");
     MG_REQUIRE(cum && chunk_state && (!mlstm || (chunk_meta && aux)), "matrix memory (chunks): scratch is missing");
     MG_REQUIRE((chunk_tokens == 32 || chunk_tokens == 64) && chunk_tokens <= mg_matrix_memory_chunk_tokens(head_dim, v_dim, mlstm),
                "matrix memory (chunks): chunks of %d tokens do not fit heads of %d and %d", chunk_tokens, head_dim, v_dim);
@@ -415,6 +446,7 @@ MG_API int mg_matrix_memory_chunked(const void* proj, int ld, int q_off, int k_o
     p.state = state; p.state_stride = state_stride; p.cum = cum; p.chunk_state = chunk_state; p.chunk_meta = chunk_meta;
     p.out = out; p.aux = aux; p.n_chunks = n_chunks; p.n_requests = n_requests; p.n_tokens = n_tokens; p.n_head = n_head;
     p.d = head_dim; p.dv = v_dim; p.L = chunk_tokens; p.n_slots = n_slots; p.constant = constant;
+    p.ssd = ssd ? 1 : 0; p.qk_group = qk_group; p.head_consts = head_consts;
     cudaStream_t s = (cudaStream_t)stream;
     if (is_bf16) return mlstm ? run_chunked<bf16, true>(p, s) : run_chunked<bf16, false>(p, s);
     return mlstm ? run_chunked<float, true>(p, s) : run_chunked<float, false>(p, s);

@@ -42,12 +42,12 @@ _SIGNATURES = {
     "mg_matrix_memory_scan": [_P, _I, _I, _I, _I, _P, _I, _P, _P, _P, _P, _P, ctypes.c_longlong, _P, _P, _I, _I, _I, _I,
                               _I, _F, _I, _I, _I, _I, _P, _P],
     "mg_matrix_memory_chunked": [_P, _I, _I, _I, _I, _P, _I, _P, _P, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _P, _P, _I,
-                                 _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
+                                 _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P, _P],
     "mg_matrix_memory_chunk_tokens": [_I, _I, _I],
     "mg_head_norm_gate": [_P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _F, _I, _I, _I, _P],
     "mg_moe_route_scored": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "mg_attention_mma": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F,
-                         _I, _I, _I, _I, _I, _I, _P, _I, _P],
+                         _I, _I, _I, _I, _I, _I, _P, _I, _F, _P, _I, _P],
     "mg_moe_route": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "mg_moe_group": [_P, _I, _I, _P, _P, _P, _P],
     "mg_moe_gemm": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P],

@@ -400,7 +400,7 @@ class CudaOps:
         mlstm = mode == "mlstm"
         out = torch.empty((n, n_head * v_dim), dtype=torch.float32, device=self.device)
         aux = torch.empty((n, n_head, 2), dtype=torch.float32, device=self.device) if mlstm else None
-        name, tokens = self._memory_chunks_name(head_dim, v_dim, mlstm) if mode != "ssd" else (None, 0)
+        name, tokens = self._memory_chunks_name(head_dim, v_dim, mlstm)
         chunks = getattr(ctx, "extra", {}).get(name) if name is not None else None
         if chunks is not None and chunks.shape[0] > 0 and self.use_chunked_memory:
             # a step with prompt portions: chunk by chunk (three kernels, every SM at work)
@@ -411,9 +411,10 @@ class CudaOps:
             meta = torch.empty((chunks.shape[0], n_head, 4), dtype=torch.float32, device=self.device) if mlstm else None
             self._run(self.lib.mg_matrix_memory_chunked(
                 _ptr(proj), proj.shape[1], q_off, k_off, v_off, _ptr(gates), gates.shape[1], _ptr(chunks), _ptr(ranges),
-                _ptr(ctx.req_ctx_before), _ptr(ctx.req_state_slot), _ptr(state), state.shape[1], _ptr(cum),
-                _ptr(chunk_state), _ptr(meta), _ptr(out), _ptr(aux), chunks.shape[0], tokens, ranges.shape[0], n, n_head,
-                head_dim, v_dim, float(constant), 1 if mlstm else 0, state.shape[0], self._is_bf16(proj), self._stream()),
+                _ptr(ctx.req_ctx_before), _ptr(ctx.req_state_slot), state.data_ptr() + 4 * int(state_offset), state.shape[1],
+                _ptr(cum), _ptr(chunk_state), _ptr(meta), _ptr(out), _ptr(aux), chunks.shape[0], tokens, ranges.shape[0], n,
+                n_head, head_dim, v_dim, float(constant), 1 if mlstm else 0, state.shape[0], self._is_bf16(proj),
+                int(qk_group), _ptr(head_consts) if mode == "ssd" else None, self._stream()),
                 "matrix memory (chunks)")
             self.launches += 2
             return out, aux
@@ -932,7 +933,7 @@ class CudaOps:
             if code != library.UNSUPPORTED:
                 self._run(code, "paged_attention (prefill, tensor cores)")
                 return out
-        if q.dtype == torch.bfloat16 and self.use_tensor_cores and self.use_mma_attention and plain:
+        if q.dtype == torch.bfloat16 and self.use_tensor_cores and self.use_mma_attention:
             # bfloat16: tiles of (token, head) rows on the warp-level tensor cores; single tokens
             # with their keys cut into ranges that a second kernel merges
             single = bool(getattr(ctx, "decode_only", False))
@@ -960,7 +961,8 @@ class CudaOps:
                     _ptr(ctx.positions), _ptr(getattr(ctx, "req_q_start", None)), _ptr(getattr(ctx, "req_q_len", None)),
                     _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(out), args[0], args[1], n, table.shape[0],
                     n_head, n_kv_head, head_dim, v_dim, cache.page_tokens, table.shape[1], int(cache.window or 0),
-                    float(scale), cache.k_pages.shape[0], *args[2:], _ptr(slopes), block, self._stream())
+                    float(scale), cache.k_pages.shape[0], *args[2:], _ptr(slopes), block, softcap, _ptr(sinks),
+                    head_dim if in_keys else 0, self._stream())
                 if code != library.UNSUPPORTED:
                     self._run(code, "paged_attention (tensor cores, general)")
                     if single and args[1] is None:

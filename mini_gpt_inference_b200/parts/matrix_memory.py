@@ -221,6 +221,12 @@ class StateSpaceDuality(Mixer):
     def cache_spec(self):
         return FixedStateSpec((self.conv_state + self.n_head * self.v_head_dim * self.state,), "float32")
 
+    def plan_step(self, batch, plan, ops) -> None:
+        # the kernel set may cut prompt portions into chunks that it scans side by side
+        planner = getattr(ops, "plan_memory_chunks", None)
+        if planner is not None:
+            planner(batch, plan, self.state, self.v_head_dim, False)
+
     def forward(self, ctx, cache, y, residual32) -> None:
         ops = ctx.ops
         if hasattr(y, "materialize"):

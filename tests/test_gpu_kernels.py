@@ -876,9 +876,9 @@ def test_refusals_are_clear(ops):
     with pytest.raises(KernelLibraryError, match="dtype"):
         ops.linear(randn(4, 8), randn(3, 8, dtype=torch.bfloat16), None, "none", torch.float32)
     with pytest.raises(KernelLibraryError, match="head_dim"):
-        cache = SimpleNamespace(k_pages=torch.zeros(2, 1, 4, 512).cuda(), v_pages=torch.zeros(2, 1, 4, 512).cuda(),
+        cache = SimpleNamespace(k_pages=torch.zeros(2, 1, 4, 2048).cuda(), v_pages=torch.zeros(2, 1, 4, 2048).cuda(),
                                 group=0, page_tokens=4, window=None)
         ctx = SimpleNamespace(block_tables=[torch.zeros(1, 2, dtype=torch.int32).cuda()],
                               token_request=torch.zeros(1, dtype=torch.int32).cuda(),
                               positions=torch.zeros(1, dtype=torch.int32).cuda())
-        ops.paged_attention(torch.zeros(1, 3 * 512).cuda(), 1, 1, 512, 1.0, cache, ctx)
+        ops.paged_attention(torch.zeros(1, 3 * 2048).cuda(), 1, 1, 2048, 1.0, cache, ctx)
