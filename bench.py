@@ -26,6 +26,8 @@ from a profiler's trace, bench/bench_kernels.py:71-116).
 
 ``--only zenedra`` prints a line of its own as well: the Zenedra decoder (layers of one mixer kind each, then
 mixed with a loop and routed experts) beside the two other designs at equal sizes.
+``--only nukodra`` likewise: the Nukodra decoder (layers of one mixer kind each, on one residual stream and on
+four; then the kinds mixed) beside Zenedra's closest layers at equal sizes.
 ``--only designs`` prints a line of its own: the Fakilorn decoder beside this decoder at equal width,
 depth, hidden width and vocabulary (random weights, two sizes): a 2,048-token prompt step, decode
 steps at the headline batch with contexts near 2,048, and the device time of every exported function
@@ -89,7 +91,7 @@ def parse_args():
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--page-tokens", type=int, default=64)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and prefill")
-    ap.add_argument("--only", choices=["all", "decode", "prefill", "serve", "kernels", "designs", "zenedra"], default="all",
+    ap.add_argument("--only", choices=["all", "decode", "prefill", "serve", "kernels", "designs", "zenedra", "nukodra"], default="all",
                     help="a small case for profilers: only the device-timed decode steps, or only "
                          "the 2,048-token prefill (the printed line is then partial); serve: 64 "
                          "requests with prompts of 16 to 512 tokens and 256 generated tokens each "
@@ -618,6 +620,67 @@ def compare_zenedra(args) -> dict:
     return out
 
 
+# ``--only nukodra``: the Nukodra decoder beside Zenedra, the closest design here (windowed attention with a
+# query and key norm and an output gate; matrix memories that run through the same scan and chunk kernels as the
+# state-space layers), at equal width, depth, head count and vocabulary (random weights).  Layers of one mixer
+# kind each with gated dense feed-forwards, so that every mixer's kernels can be read off alone: windowed
+# attention with capped scores, sinks and rotary positions; attention over cached latents (heads of 128 + 64
+# features over latents of 512, every second layer reading the latents of the layer before it); Mamba-2 with a
+# state of 128 rows.  Then the three kinds mixed on four residual streams, one layer without a feed-forward.
+def _nukodra_raw(sz: dict, kinds: list, streams) -> dict:
+    heads = sz["heads"]
+    mixers = {
+        "attention": {"heads": heads, "kv_heads": sz["kv_heads"], "dim": 64, "vdim": 64, "scale": 0.125,
+                      "mask": {"size": 512}, "rot": {"dims": 64, "base": 10000.0}, "softcap": 30.0},
+        "latent_attention": {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512,
+                             "scale": 192 ** -0.5, "rot": {"dims": 64, "base": 10000.0}},
+        "mamba2": {"heads": 2 * sz["width"] // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1},
+    }
+    dense = {"kind": "dense", "ff": sz["ff"] * 2 // 3 // 64 * 64}
+    layers, last_latent = [], None
+    for i, kind in enumerate(kinds):
+        mixer = dict(mixers[kind])
+        if kind == "latent_attention":
+            if last_latent is not None and i % 2:
+                mixer["kv_from"] = last_latent
+            else:
+                last_latent = i
+        layers.append({"type": kind, "mixer": mixer, "mlp": None if (streams and kind == "mamba2") else dense})
+    raw = {"architecture": "Nukodra", "vocab": sz["vocab"], "width": sz["width"], "layers": layers, "norm": {"eps": 1e-5}}
+    if streams:
+        raw["streams"] = streams
+    return raw
+
+
+def compare_nukodra(args) -> dict:
+    import torch
+
+    from mini_gpt_inference_b200 import NukodraConfig, ZenedraConfig
+    from mini_gpt_inference_b200.kernels.ops import default_ops
+
+    ops = default_ops("cuda:0")
+    batch, context, prompt_len = args.batch, 2048, PREFILL_TOKENS
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda:0")
+    out = {"impl": "ours", "partial": "nukodra beside zenedra", "dtype": args.dtype, "batch": batch,
+           "context": context, "prompt": prompt_len, "rows": []}
+    for size_name, sz in DESIGN_SIZES.items():
+        n = sz["layers"]
+        for name, kinds in (("attention, dense", ["attention"] * n), ("gla, dense", ["gla"] * n)):
+            cfg = ZenedraConfig.from_dict(_zenedra_raw(sz, kinds, False, False, context))
+            out["rows"].append(_measure_design(args, ops, flush, f"zenedra {size_name} {name}", cfg, batch, context,
+                                               prompt_len))
+        mixed = (["mamba2", "latent_attention", "attention", "latent_attention"] * n)[:n]
+        for name, kinds, streams in (("attention, dense", ["attention"] * n, None),
+                                     ("latent attention, dense", ["latent_attention"] * n, None),
+                                     ("mamba2, dense", ["mamba2"] * n, None),
+                                     ("attention, dense, 4 streams", ["attention"] * n, 4),
+                                     ("mixed, 4 streams", mixed, 4)):
+            cfg = NukodraConfig.from_dict(_nukodra_raw(sz, kinds, streams))
+            out["rows"].append(_measure_design(args, ops, flush, f"nukodra {size_name} {name}", cfg, batch, context,
+                                               prompt_len))
+    return out
+
+
 def check_decode_logits(args) -> dict:
     """Outside every timed region: the decode step that the benchmark times (batch 8, contexts of
     2,048, the replayed graph) is run once on fixed tokens and its logits are compared with rows
@@ -681,6 +744,8 @@ def run_ours(args) -> dict:
         return compare_designs(args)
     if args.only == "zenedra":
         return compare_zenedra(args)
+    if args.only == "nukodra":
+        return compare_nukodra(args)
     if args.only == "decode":
         cfg, windows, launches, mean_ctx, clocks = device_decode(args, args.batch, args.steps, args.warmup,
                                                                  min_seconds=0.0)
