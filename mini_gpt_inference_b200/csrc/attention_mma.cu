@@ -561,6 +561,273 @@ __global__ void attention_merge_kernel(const AttnParams p) {
     }
 }
 
+
+// ---- wide rows that hold their own values ------------------------------------------------------------
+// Key rows of several hundred features whose first dv features are also the values (cached latents): too wide for
+// query fragments and a whole row of results in one warp's registers.  A CTA of eight warps takes 32 rows, (token,
+// head of the group) pairs in token order, and walks blocks of 64 keys (two buffers in turn).  The queries wait in
+// shared memory.  Warp (rg, cg) takes rows 16 rg .. 16 rg + 15: it multiplies them with keys 16 cg .. 16 cg + 15 of the
+// block, the four warps of a row group exchange their maxima through shared memory, each keeps the sum of its own
+// keys' weights (the sums meet after the last block), the weights go to shared memory as bfloat16, and the warp
+// then adds the block's 64 keys into columns CW cg .. CW cg + CW - 1 of its rows' results.  `single`: the rows are one
+// token's heads and the CTA takes one range of its keys; results go to scratch as the merge kernel reads them.
+constexpr int WIDE_ROWS = 32;
+
+template <int CW>
+__global__ void __launch_bounds__(256, 1)
+attention_wide_kernel(const AttnParams p, const int single, const int dpad, const int row_tiles) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    const int stride = dpad + PAD;
+    bf16* qs = reinterpret_cast<bf16*>(smem_raw);                     // [32][stride]
+    bf16* kbuf = qs + WIDE_ROWS * stride;                              // [2][KB][stride]
+    bf16* ps = kbuf + 2 * KB * stride;                                 // [32][KB + PAD]
+    float* mx = reinterpret_cast<float*>(ps + WIDE_ROWS * (KB + PAD)); // [4][32]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, rg = warp & 1, cg = warp >> 1;
+    // columns d .. dpad of the key rows are never loaded: zeros, once
+    if (p.d < dpad) {
+        const int extra = dpad - p.d;
+        for (int i = tid; i < 2 * KB * extra; i += 256) kbuf[(i / extra) * stride + p.d + i % extra] = __float2bfloat16_rn(0.f);
+    }
+    pdl_trigger();
+    pdl_wait();
+    const int kv_head = blockIdx.y, group = p.n_head / p.n_kv_head;
+    int request, first_token, row_base, rows_total, j_first, j_last, lo_all;
+    if (single) {
+        const int token = blockIdx.x / row_tiles, split = blockIdx.z;
+        int position = p.positions[token];
+        if (position < 0) return;                                      // padding: the merge writes its zeros
+        if (!MG_GUARDED(attention_mma, MG_GUARD_POSITION, position, (long long)p.max_pages * p.page_tokens)) position = 0;
+        lo_all = first_visible(p, position);
+        const int live = (position - (lo_all / KB) * KB) / p.split_keys + 1;
+        if (split >= live) return;
+        j_first = (lo_all / KB) * KB + split * p.split_keys;
+        j_last = min(position, j_first + p.split_keys - 1);
+        request = p.token_request[token];
+        if (!MG_GUARDED(attention_mma, MG_GUARD_REQUEST, request, p.n_requests)) request = 0;
+        first_token = token;
+        row_base = (blockIdx.x % row_tiles) * WIDE_ROWS;
+        rows_total = group;
+    } else {
+        int tile = (int)(gridDim.x - 1 - blockIdx.x);                   // the last tiles, which see the most keys, first
+        for (request = 0; request < p.n_requests; ++request) {
+            const int tiles = (p.req_q_len[request] * group + WIDE_ROWS - 1) / WIDE_ROWS;
+            if (tile < tiles) break;
+            tile -= tiles;
+        }
+        if (request >= p.n_requests) return;
+        first_token = p.req_q_start[request];
+        row_base = tile * WIDE_ROWS;
+        rows_total = p.req_q_len[request] * group;
+        const int last_row = min(rows_total, row_base + WIDE_ROWS) - 1;
+        int hi = p.positions[first_token + last_row / group];
+        if (hi < 0) return;                                            // padding
+        if (!MG_GUARDED(attention_mma, MG_GUARD_POSITION, hi, (long long)p.max_pages * p.page_tokens)) hi = 0;
+        lo_all = p.window > 0 ? first_visible(p, max(0, p.positions[first_token + row_base / group])) : 0;
+        j_first = (lo_all / KB) * KB;
+        j_last = hi;
+    }
+    const int* table = p.block_table + (size_t)request * p.max_pages;
+
+    // the queries of the tile's rows; rows without a token and columns beyond d as zeros
+    {
+        const int chunks = dpad >> 3;
+        for (int i = tid; i < WIDE_ROWS * chunks; i += 256) {
+            const int r = i / chunks, c = (i - r * chunks) * 8, row = row_base + r;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (row < rows_total && c < p.d) {
+                const int t = single ? 0 : row / group, h = single ? row : row - t * group;
+                v = *reinterpret_cast<const uint4*>(p.q + (size_t)(first_token + t) * p.q_stride + (size_t)(kv_head * group + h) * p.d + c);
+            }
+            *reinterpret_cast<uint4*>(qs + r * stride + c) = v;
+        }
+    }
+    // this lane's two rows
+    int pos[2], lo[2], token[2], head[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = row_base + rg * 16 + (lane >> 2) + 8 * r;
+        const bool live = row < rows_total;
+        const int t = (single || !live) ? 0 : row / group;
+        token[r] = first_token + t;
+        head[r] = kv_head * group + (live ? row - t * group : 0);
+        pos[r] = live ? p.positions[token[r]] : -1;
+        lo[r] = pos[r] >= 0 ? first_visible(p, pos[r]) : 0;
+    }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f}, o[CW / 8][4];
+#pragma unroll
+    for (int n = 0; n < CW / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+
+    const int page_shift = (p.page_tokens & (p.page_tokens - 1)) == 0 ? __ffs(p.page_tokens) - 1 : -1;
+    const int chunks = p.d >> 3;
+    // a warp copies eight of a block's keys, a row's 16-byte chunks across its lanes
+    auto load_keys = [&](int j0, bf16* dst) {
+        for (int key = warp * 8; key < warp * 8 + 8; ++key) {
+            const int j = j0 + key;
+            const bool real = j >= lo_all && j <= j_last;
+            size_t row = 0;
+            if (real) {
+                const int index = page_shift >= 0 ? j >> page_shift : j / p.page_tokens;
+                const int within = page_shift >= 0 ? j & (p.page_tokens - 1) : j - index * p.page_tokens;
+                int page = table[index];
+                if (!MG_GUARDED(attention_mma, MG_GUARD_PAGE, page, p.num_pages)) page = 0;
+                row = ((size_t)page * p.n_kv_head + kv_head) * p.page_tokens + within;
+            }
+            for (int c = lane; c < chunks; c += 32) cp_async16(dst + key * stride + c * 8, p.k_pages + row * p.d + c * 8, real);
+        }
+    };
+    load_keys(j_first, kbuf);
+    cp_async_commit();
+    int buf = 0;
+    for (int j0 = j_first; j0 <= j_last; j0 += KB, buf ^= 1) {
+        cp_async_wait<0>();
+        __syncthreads();                                   // the block is here; everyone has left the one before
+        if (j0 + KB <= j_last) {
+            load_keys(j0 + KB, kbuf + (buf ^ 1) * KB * stride);
+            cp_async_commit();
+        }
+        const bf16* kb = kbuf + buf * KB * stride;
+        float s[2][4];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+        const bf16* a_ptr = qs + (rg * 16 + (lane & 15)) * stride + (lane >> 4) * 8;
+        const bf16* b_ptr = kb + (cg * 16 + (lane >> 4) * 8 + (lane & 7)) * stride + ((lane >> 3) & 1) * 8;
+#pragma unroll 4
+        for (int kk = 0; kk < dpad; kk += 16) {
+            uint32_t a[4], b[4];
+            ldsm4(a, a_ptr + kk);
+            ldsm4(b, b_ptr + kk);
+            mma16816(s[0], a, b[0], b[1]);
+            mma16816(s[1], a, b[2], b[3]);
+        }
+        float bm[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = j0 + cg * 16 + n * 8 + 2 * (lane & 3) + (e & 1), r = e >> 1;
+                float sc = s[n][e] * p.scale_log2;
+                if (p.cap_log2 > 0.f) sc = p.cap_log2 * tanhf(sc / p.cap_log2);
+                const float v = (j <= pos[r] && j >= lo[r]) ? sc : -INFINITY;
+                s[n][e] = v;
+                bm[r] = fmaxf(bm[r], v);
+            }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            bm[r] = fmaxf(bm[r], __shfl_xor_sync(0xffffffffu, bm[r], 1));
+            bm[r] = fmaxf(bm[r], __shfl_xor_sync(0xffffffffu, bm[r], 2));
+            if ((lane & 3) == 0) mx[cg * WIDE_ROWS + rg * 16 + (lane >> 2) + 8 * r] = bm[r];
+        }
+        __syncthreads();
+        float corr[2], base[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int row = rg * 16 + (lane >> 2) + 8 * r;
+            const float all = fmaxf(fmaxf(mx[row], mx[WIDE_ROWS + row]), fmaxf(mx[2 * WIDE_ROWS + row], mx[3 * WIDE_ROWS + row]));
+            const float nm = fmaxf(m[r], all);
+            corr[r] = (m[r] == -INFINITY) ? 0.f : exp2_approx(m[r] - nm);
+            base[r] = (nm == -INFINITY) ? 0.f : nm;
+            m[r] = nm;
+        }
+        float bs[2] = {0.f, 0.f};
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float pr = exp2_approx(s[n][e] - base[e >> 1]);
+                s[n][e] = pr;
+                bs[e >> 1] += pr;
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r)
+                *reinterpret_cast<uint32_t*>(ps + (rg * 16 + (lane >> 2) + 8 * r) * (KB + PAD) + cg * 16 + n * 8 + 2 * (lane & 3)) =
+                    pack_bf16(s[n][2 * r], s[n][2 * r + 1]);
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            bs[r] += __shfl_xor_sync(0xffffffffu, bs[r], 1);
+            bs[r] += __shfl_xor_sync(0xffffffffu, bs[r], 2);
+            l[r] = l[r] * corr[r] + bs[r];
+        }
+#pragma unroll
+        for (int n = 0; n < CW / 8; ++n) {
+            o[n][0] *= corr[0];
+            o[n][1] *= corr[0];
+            o[n][2] *= corr[1];
+            o[n][3] *= corr[1];
+        }
+        __syncthreads();                                   // all 64 keys' weights of the warp's rows are there
+#pragma unroll
+        for (int kk = 0; kk < KB / 16; ++kk) {
+            uint32_t a[4];
+            ldsm4(a, ps + (rg * 16 + (lane & 15)) * (KB + PAD) + kk * 16 + (lane >> 4) * 8);
+            const bf16* v_ptr = kb + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * stride + cg * CW + (lane >> 4) * 8;
+#pragma unroll
+            for (int n = 0; n < CW / 8; n += 2) {
+                uint32_t b[4];
+                ldsm4_t(b, v_ptr + n * 8);
+                mma16816(o[n], a, b[0], b[1]);
+                mma16816(o[n + 1], a, b[2], b[3]);
+            }
+        }
+    }
+    // the four warps of a row group kept the sums of their own keys: they meet here
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+        if ((lane & 3) == 0) mx[cg * WIDE_ROWS + rg * 16 + (lane >> 2) + 8 * r] = l[r];
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        if (pos[r] < 0) continue;
+        const int row = rg * 16 + (lane >> 2) + 8 * r;
+        float sum = mx[row] + mx[WIDE_ROWS + row] + mx[2 * WIDE_ROWS + row] + mx[3 * WIDE_ROWS + row];
+        if (single) {
+            const size_t slot = ((size_t)token[r] * p.n_head + head[r]) * p.splits + blockIdx.z;
+            if (cg == 0 && (lane & 3) == 0) {
+                p.part_ml[slot * 2] = m[r];
+                p.part_ml[slot * 2 + 1] = sum;
+            }
+#pragma unroll
+            for (int n = 0; n < CW / 8; ++n) {
+                const int c = cg * CW + n * 8 + 2 * (lane & 3);
+                if (c >= p.dv) continue;
+                *reinterpret_cast<float2*>(p.part_o + slot * p.dv + c) = make_float2(o[n][2 * r], o[n][2 * r + 1]);
+            }
+            continue;
+        }
+        sum += sink_term(p, head[r], m[r]);
+        const float inv = sum > 0.f ? 1.0f / sum : 0.f;
+        bf16* orow = p.out + (size_t)token[r] * p.n_head * p.dv + (size_t)head[r] * p.dv;
+        const bf16* grow = p.gate ? p.gate + (size_t)token[r] * p.gate_stride + (size_t)head[r] * p.dv : nullptr;
+#pragma unroll
+        for (int n = 0; n < CW / 8; ++n) {
+            const int c = cg * CW + n * 8 + 2 * (lane & 3);
+            if (c >= p.dv) continue;
+            float a = o[n][2 * r] * inv, b = o[n][2 * r + 1] * inv;
+            if (grow) {
+                const __nv_bfloat162 g = *reinterpret_cast<const __nv_bfloat162*>(grow + c);
+                a *= logistic(__bfloat162float(g.x));
+                b *= logistic(__bfloat162float(g.y));
+            }
+            *reinterpret_cast<uint32_t*>(orow + c) = pack_bf16(a, b);
+        }
+    }
+}
+
+template <int CW>
+int launch_wide(const AttnParams& p, int single, int n_tiles, int dpad, size_t smem, cudaStream_t s) {
+    const int group = p.n_head / p.n_kv_head, row_tiles = (group + WIDE_ROWS - 1) / WIDE_ROWS;
+    cudaError_t e = cudaFuncSetAttribute(attention_wide_kernel<CW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) {
+        const dim3 grid = single ? dim3(p.n_tokens * row_tiles, p.n_kv_head, p.splits) : dim3(n_tiles, p.n_kv_head);
+        e = mg_launch(attention_wide_kernel<CW>, grid, dim3(256), smem, s, true, p, single, dpad, row_tiles);
+    }
+    if (e == cudaSuccess && single)
+        e = mg_launch(attention_merge_kernel, dim3(p.n_tokens, p.n_head), dim3(128), 0, s, true, p);
+    if (e != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "attention (wide rows): %s", cudaGetErrorString(e));
+    return MG_OK;
+}
+
 template <int DP, int DVP>
 int launch(const AttnParams& p, int single_tokens, int n_tiles, cudaStream_t s) {
     size_t smem = (size_t)2 * KB * (DP + PAD + DVP + PAD) * sizeof(bf16);      // two buffers
@@ -650,4 +917,54 @@ MG_API int mg_attention_mma(const void* q, int q_stride, const void* k_pages, co
     if (dp == 96) return launch<96, 128>(p, single_tokens, n_tiles, s);
     if (dvp == 64) return launch<128, 64>(p, single_tokens, n_tiles, s);
     return launch<128, 128>(p, single_tokens, n_tiles, s);
+}
+
+// Rows of 32 (token, head) pairs that the wide-row kernel takes for a prompt portion of `tokens` tokens.
+MG_API int mg_attention_wide_tiles(int tokens, int group) { return (tokens * group + WIDE_ROWS - 1) / WIDE_ROWS; }
+
+// Attention over key rows of d features whose first dv features are the values (one row per token and key/value
+// head, k_pages [page, G, page_tokens, d]); the other arguments as mg_attention_mma.  single_tokens = 1: splits ranges
+// of split_keys keys, scratch of mg_attention_mma_scratch_floats floats, merged by a second kernel; 0: n_tiles is the
+// sum of mg_attention_wide_tiles over the requests.  Returns MG_ERR_UNSUPPORTED for sizes it does not take.
+MG_API int mg_attention_wide(const void* q, int q_stride, const void* k_pages, const int* block_table, const int* token_request,
+                             const int* positions, const int* req_q_start, const int* req_q_len, const void* gate,
+                             int gate_stride, void* out, float* scratch, int n_tokens, int n_requests, int n_head, int n_kv_head,
+                             int d, int dv, int page_tokens, int max_pages, int window, float scale, int num_pages,
+                             int single_tokens, int n_tiles, int splits, int split_keys, float softcap, const float* sinks,
+                             void* stream) {
+    if (n_tokens == 0) return MG_OK;
+    MG_REQUIRE(n_tokens > 0 && n_head > 0 && n_kv_head > 0 && n_head % n_kv_head == 0 && page_tokens > 0 && max_pages > 0 &&
+               dv > 0 && dv <= d, "attention (wide rows): bad sizes");
+    const bool aligned = d % 8 == 0 && dv % 8 == 0 && q_stride % 8 == 0 && (gate == nullptr || gate_stride % 2 == 0) &&
+                         ((uintptr_t)q % 16 == 0) && ((uintptr_t)k_pages % 16 == 0) && ((uintptr_t)out % 4 == 0) &&
+                         ((uintptr_t)gate % 4 == 0);
+    const int dpad = (d + 15) / 16 * 16;
+    const size_t smem = ((size_t)(WIDE_ROWS + 2 * KB) * (dpad + PAD) + WIDE_ROWS * (KB + PAD)) * sizeof(bf16) + 4 * WIDE_ROWS * sizeof(float);
+    if (!aligned || dv > 512 || smem > 227 * 1024 || n_kv_head > 65535) return MG_ERR_UNSUPPORTED;
+    AttnParams p;
+    p.q = (const bf16*)q; p.q_stride = q_stride; p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)k_pages;
+    p.block_table = block_table; p.token_request = token_request; p.positions = positions;
+    p.req_q_start = req_q_start; p.req_q_len = req_q_len; p.gate = (const bf16*)gate; p.gate_stride = gate_stride;
+    p.out = (bf16*)out; p.part_o = nullptr; p.part_ml = nullptr; p.counters = nullptr;
+    p.n_tokens = n_tokens; p.n_requests = n_requests; p.n_head = n_head; p.n_kv_head = n_kv_head; p.d = d; p.dv = dv;
+    p.page_tokens = page_tokens; p.max_pages = max_pages; p.window = window > 0 ? window : 0; p.num_pages = num_pages;
+    p.tile_tokens = 0; p.splits = splits; p.split_keys = split_keys; p.scale_log2 = scale * LOG2E;
+    p.slopes = nullptr; p.block = 0;
+    p.cap_log2 = softcap > 0.f ? softcap * LOG2E : 0.f; p.sinks = sinks; p.v_stride = d;
+    if (single_tokens) {
+        MG_REQUIRE(scratch != nullptr && splits > 0 && splits <= 65535 && split_keys > 0 && split_keys % KB == 0,
+                   "attention: the ranges of keys want scratch and sizes that are multiples of %d", KB);
+        p.part_o = scratch;
+        p.part_ml = scratch + (size_t)n_tokens * n_head * splits * dv;
+    } else {
+        MG_REQUIRE(req_q_start && req_q_len && n_tiles > 0, "attention (wide rows): no tiles");
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    // the values' columns, padded, in four equal parts of whole pairs of 8-column tiles; padded columns lie inside
+    // the padded key row (dv <= d) or, beyond it, in the row's padding and the next row: they are never stored
+    if (dv <= 64 && dpad >= 64) return launch_wide<16>(p, single_tokens, n_tiles, dpad, smem, s);
+    if (dv <= 128 && dpad >= 128) return launch_wide<32>(p, single_tokens, n_tiles, dpad, smem, s);
+    if (dv <= 256 && dpad >= 256) return launch_wide<64>(p, single_tokens, n_tiles, dpad, smem, s);
+    if (dpad >= 512) return launch_wide<128>(p, single_tokens, n_tiles, dpad, smem, s);
+    return MG_ERR_UNSUPPORTED;
 }

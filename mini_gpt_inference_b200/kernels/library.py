@@ -48,6 +48,9 @@ _SIGNATURES = {
     "mg_moe_route_scored": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "mg_attention_mma": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F,
                          _I, _I, _I, _I, _I, _I, _P, _I, _F, _P, _I, _P],
+    "mg_attention_wide": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I,
+                          _I, _I, _F, _P, _P],
+    "mg_attention_wide_tiles": [_I, _I],
     "mg_moe_route": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "mg_moe_group": [_P, _I, _I, _P, _P, _P, _P],
     "mg_moe_gemm": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P],

@@ -968,6 +968,33 @@ class CudaOps:
                     if single and args[1] is None:
                         self.launches += 1                       # the merge of the ranges as a kernel of its own
                     return out
+        if q.dtype == torch.bfloat16 and self.use_tensor_cores and self.use_mma_attention and in_keys and not biased:
+            # rows too wide for that kernel's registers (cached latents of several hundred features): tiles of 32
+            # (token, head) rows whose queries wait in shared memory
+            single = bool(getattr(ctx, "decode_only", False))
+            q_len = getattr(ctx, "host_q_len", None)
+            group = n_head // n_kv_head
+            args = None
+            if single:
+                keys = self.lib.mg_attention_mma_split_keys(int(ctx.max_ctx_after))
+                splits = max(1, -(-int(ctx.max_ctx_after) // keys))
+                floats = self.lib.mg_attention_mma_scratch_floats(n, n_head, v_dim, splits)
+                scratch = torch.empty((floats,), dtype=torch.float32, device=self.device)
+                args = [_ptr(scratch), 1, 0, splits, keys]
+            elif q_len and getattr(ctx, "req_q_start", None) is not None:
+                args = [None, 0, sum(self.lib.mg_attention_wide_tiles(int(t), group) for t in q_len), 0, 0]
+            if args is not None:
+                code = self.lib.mg_attention_wide(
+                    _ptr(q), q.shape[1], _ptr(cache.k_pages), _ptr(table), _ptr(ctx.token_request), _ptr(ctx.positions),
+                    _ptr(getattr(ctx, "req_q_start", None)), _ptr(getattr(ctx, "req_q_len", None)), _ptr(gate),
+                    gate.stride(0) if gate is not None else 0, _ptr(out), args[0], n, table.shape[0], n_head, n_kv_head,
+                    head_dim, v_dim, cache.page_tokens, table.shape[1], int(cache.window or 0), float(scale),
+                    cache.k_pages.shape[0], *args[1:], softcap, _ptr(sinks), self._stream())
+                if code != library.UNSUPPORTED:
+                    self._run(code, "paged_attention (tensor cores, wide rows)")
+                    if single:
+                        self.launches += 1                       # the merge of the ranges
+                    return out
         self._run(self.lib.mg_paged_attention_general(
             _ptr(q), q.shape[1], _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(table), _ptr(ctx.token_request),
             _ptr(ctx.positions), _ptr(out), n, n_head, n_kv_head, head_dim, v_dim, _ptr(gate),

@@ -282,3 +282,120 @@ def test_command_line_writes_and_generates(tmp_path):
     assert run.returncode == 0, run.stderr[-2000:]
     out = json.loads(run.stdout.strip().splitlines()[-1])
     assert out["token_ids"] == plain_greedy(raw, load_file(folder / "model.safetensors"), prompt, 8)
+
+
+class _AttentionContext:
+    """The few fields of a step's context that the attention kernels read."""
+
+    def __init__(self, tables, token_request, positions, q_len, decode_only):
+        to = lambda rows: torch.tensor(rows, dtype=torch.int32, device="cuda:0")
+        self.block_tables = [to(tables)]
+        self.token_request, self.positions = to(token_request), to(positions)
+        self.req_q_start = to([sum(q_len[:i]) for i in range(len(q_len))])
+        self.req_q_len = to(q_len)
+        self.host_q_len = list(q_len)
+        self.decode_only = decode_only
+        self.max_ctx_after = max(positions) + 1
+
+
+@pytest.mark.parametrize("path", ["tiles", "ranges"])
+@pytest.mark.parametrize("heads,d,dv,pt", [(5, 160, 128, 16), (16, 576, 512, 64), (40, 80, 48, 8), (3, 520, 264, 32)])
+def test_attention_over_wide_rows_that_hold_their_values(path, heads, d, dv, pt):
+    """One key row per token, shared by all heads, whose first features are the values, wider than the warp-tile
+    kernel's registers take: portions of two requests, and single tokens over ranges of keys.  Every query is made
+    to favour one key far back (the first, one at a page's last row, one in the middle), among hundreds."""
+    import math
+
+    from mini_gpt_inference_b200.cache.storage import PagedKVView
+    from mini_gpt_inference_b200.kernels.ops import default_ops
+
+    ops = default_ops("cuda:0")
+    gen = torch.Generator().manual_seed(heads * d + dv)
+    lengths = [333, 70]
+    n_pages = [-(-n // pt) for n in lengths]
+    order = torch.randperm(sum(n_pages) + 3, generator=gen).tolist()
+    tables = [order[:n_pages[0]] + [0] * (max(n_pages) - n_pages[0]), order[n_pages[0]: sum(n_pages)] + [0] * (max(n_pages) - n_pages[1])]
+    rows_all = [torch.randn(n, d, generator=gen).bfloat16().float() for n in lengths]
+    if path == "tiles":
+        rows = [(0, p) for p in range(300, 333)] + [(1, p) for p in range(0, 70)]
+        q_len = [33, 70]
+    else:
+        rows = [(0, 332), (1, 69)]
+        q_len = [1, 1]
+    targets = [[0, pt * max(1, p // pt) - 1 if p >= pt else 0, p // 2][i % 3] for i, (_, p) in enumerate(rows)]
+    for (r, _), j in zip(rows, targets):
+        rows_all[r][j, dv:] = 3.0 * torch.sign(rows_all[r][j, dv:])       # a long key part outside the values
+    pages = torch.full((len(order), 1, pt, d), float("nan"))
+    for r, n in enumerate(lengths):
+        for j in range(n):
+            pages[tables[r][j // pt], 0, j % pt] = rows_all[r][j]
+    n = len(rows)
+    q = 0.3 * torch.randn(n, heads, d, generator=gen)
+    for i, ((r, _), j) in enumerate(zip(rows, targets)):
+        q[i] += 0.3 * rows_all[r][j]
+    q_rows = torch.cat([q.reshape(n, -1), torch.randn(n, 16, generator=gen)], dim=1).bfloat16()
+    gate = torch.randn(n, heads * dv, generator=gen).bfloat16()
+    sinks = torch.randn(heads, generator=gen) + 2.0
+    scale = 1.0 / math.sqrt(d)
+    k_dev = pages.to(device="cuda:0", dtype=torch.bfloat16)
+    cache = PagedKVView(k_dev, k_dev, 0, pt, None, False, values_in_keys=True)
+    ctx = _AttentionContext(tables, [r for r, _ in rows], [p for _, p in rows], q_len, path == "ranges")
+    launches = ops.launches
+    got = ops.paged_attention_general(q_rows.cuda(), heads, 1, d, dv, scale, cache, ctx, gate=gate.cuda(), sinks=sinks.cuda())
+    assert ops.launches - launches == (1 if path == "tiles" else 2)       # tensor-core kernels, not the general one
+    ops.use_mma_attention = False
+    try:
+        general = ops.paged_attention_general(q_rows.cuda(), heads, 1, d, dv, scale, cache, ctx, gate=gate.cuda(), sinks=sinks.cuda())
+    finally:
+        ops.use_mma_attention = True
+    want = torch.empty(n, heads, dv, dtype=torch.float64)
+    peak = []
+    for i, (r, p) in enumerate(rows):
+        keys = rows_all[r][: p + 1].double()
+        for h in range(heads):
+            s = (keys @ q_rows[i, h * d: (h + 1) * d].double()) * scale
+            top = max(float(s.max()), float(sinks[h]))
+            w = torch.exp(s - top)
+            w = w / (w.sum() + math.exp(float(sinks[h]) - top))
+            peak.append(float(w[targets[i]]))
+            want[i, h] = w @ keys[:, :dv]
+    assert min(peak) > 0.4                                   # the chosen key does carry the weight
+    want = want.view(n, -1) * torch.sigmoid(gate.double())
+    assert torch.allclose(general.double().cpu(), want, atol=3e-2, rtol=3e-2)
+    assert torch.allclose(got.double().cpu(), want, atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("tokens", [1, 5, 16, 150])
+@pytest.mark.parametrize("heads,n_in,n_out", [(3, 24, 40), (5, 72, 136), (2, 200, 16), (4, 20, 12)])
+def test_one_small_matrix_per_head(dtype, tokens, heads, n_in, n_out):
+    """Both layouts of the heads' matrices (a head's rows as its outputs, or as its inputs), inputs at an offset
+    inside wider rows, outputs into a wider buffer, with and without the gate; few tokens and many (bfloat16 steps
+    of 16 tokens and more run on the tensor cores)."""
+    from mini_gpt_inference_b200.kernels.ops import default_ops
+
+    ops = default_ops("cuda:0")
+    t = torch.float32 if dtype == "float32" else torch.bfloat16
+    gen = torch.Generator().manual_seed(tokens * heads + n_in)
+    x_head = n_in + 8
+    x = torch.randn(tokens, 16 + heads * x_head, generator=gen).to(t)
+    gate = torch.randn(tokens, heads * n_out, generator=gen).to(t)
+    xs = torch.stack([x[:, 16 + h * x_head: 16 + h * x_head + n_in] for h in range(heads)], 1).double()     # [n, h, i]
+    tol = 1e-5 if dtype == "float32" else 2e-2
+    for rows_are_inputs in (False, True):
+        w = (torch.randn(heads * (n_in if rows_are_inputs else n_out), n_out if rows_are_inputs else n_in, generator=gen)
+             / n_in ** 0.5).to(t)
+        per_head = w.double().view(heads, n_in, n_out) if rows_are_inputs else w.double().view(heads, n_out, n_in).transpose(1, 2)
+        want = torch.einsum("nhi,hij->nhj", xs, per_head)
+        got = ops.head_linear(x.cuda(), 16, x_head, w.cuda(), rows_are_inputs, heads, n_in, n_out)
+        assert torch.allclose(got.double().cpu().view(tokens, heads, n_out), want, atol=tol, rtol=tol)
+        got = ops.head_linear(x.cuda(), 16, x_head, w.cuda(), rows_are_inputs, heads, n_in, n_out, gate=gate.cuda())
+        gated = want * torch.sigmoid(gate.double()).view(tokens, heads, n_out)
+        assert torch.allclose(got.double().cpu().view(tokens, heads, n_out), gated, atol=tol, rtol=tol)
+        wide = torch.full((tokens, 8 + heads * (n_out + 4)), 7.0, dtype=t, device="cuda:0")
+        ops.head_linear(x.cuda(), 16, x_head, w.cuda(), rows_are_inputs, heads, n_in, n_out, out=wide, out_off=8, out_head=n_out + 4)
+        back = wide.double().cpu()
+        for h in range(heads):
+            lo = 8 + h * (n_out + 4)
+            assert torch.allclose(back[:, lo: lo + n_out], want[:, h], atol=tol, rtol=tol)
+            assert bool((back[:, lo + n_out: lo + n_out + 4] == 7.0).all())       # nothing written between the heads
