@@ -49,6 +49,99 @@ causal_conv_silu_kernel(const T* __restrict__ x, int ld, int x_off, const float*
     out[(size_t)token * channels + c] = from_float<T>(acc / (1.0f + expf(-acc)));
 }
 
+// Eight neighbouring channels and TT consecutive tokens of the step per thread, 16-byte loads and stores; each
+// output's sum runs over the taps in the same rising order as in the kernel above, so both give the same bits.
+template <typename T>
+__device__ __forceinline__ void load8(float (&v)[8], const T* p);
+template <>
+__device__ __forceinline__ void load8<float>(float (&v)[8], const float* p) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<bf16>(float (&v)[8], const bf16* p) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        v[2 * u] = __bfloat162float(h[u].x);
+        v[2 * u + 1] = __bfloat162float(h[u].y);
+    }
+}
+__device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void store8(bf16* p, const float (&v)[8]) {
+    uint4 raw;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) h[u] = __floats2bfloat162_rn(v[2 * u], v[2 * u + 1]);
+    *reinterpret_cast<uint4*>(p) = raw;
+}
+
+template <typename T, int TT>
+__global__ void __launch_bounds__(THREADS)
+causal_conv_silu_vec_kernel(const T* __restrict__ x, int ld, int x_off, const float* __restrict__ taps,
+                            const float* __restrict__ bias, const int* __restrict__ token_request,
+                            const int* __restrict__ positions, const int* __restrict__ req_q_start,
+                            const int* __restrict__ req_ctx_before, const int* __restrict__ req_state_slot,
+                            const float* __restrict__ state, long long state_stride, T* __restrict__ out, int channels,
+                            int n_taps, int n_requests, int n_slots, int n_tokens) {
+    pdl_trigger();
+    pdl_wait();
+    const int c = (blockIdx.x * THREADS + threadIdx.x) * 8, t0 = blockIdx.y * TT;
+    if (c >= channels) return;
+    int start[TT], local[TT];
+    const float* old[TT];                                  // null: zeros before the sequence's start
+    bool live[TT];
+    float acc[TT][8];
+#pragma unroll
+    for (int tt = 0; tt < TT; ++tt) {
+        const int token = t0 + tt;
+        live[tt] = token < n_tokens && positions[token] >= 0;
+        start[tt] = local[tt] = 0;
+        old[tt] = nullptr;
+        if (live[tt]) {
+            int r = token_request[token];
+            if (!MG_GUARDED(short_conv, MG_GUARD_REQUEST, r, n_requests)) { live[tt] = false; continue; }
+            int slot = req_state_slot[r];
+            if (!MG_GUARDED(short_conv, MG_GUARD_ROW, slot, n_slots)) { live[tt] = false; continue; }
+            start[tt] = req_q_start[r];
+            local[tt] = token - start[tt];
+            if (req_ctx_before[r] != 0) old[tt] = state + (size_t)slot * state_stride;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc[tt][u] = bias ? bias[c + u] : 0.f;
+    }
+    for (int j = 0; j < n_taps; ++j) {
+        float w[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) w[u] = taps[(size_t)(c + u) * n_taps + j];
+#pragma unroll
+        for (int tt = 0; tt < TT; ++tt) {
+            if (!live[tt]) continue;
+            const int back = local[tt] - (n_taps - 1) + j;
+            float v[8];
+            if (back >= 0) load8<T>(v, x + (size_t)(start[tt] + back) * ld + x_off + c);
+            else if (old[tt]) load8<float>(v, old[tt] + (size_t)(n_taps - 1 + back) * channels + c);
+            else {
+#pragma unroll
+                for (int u = 0; u < 8; ++u) v[u] = 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) acc[tt][u] = fmaf(w[u], v[u], acc[tt][u]);
+        }
+    }
+#pragma unroll
+    for (int tt = 0; tt < TT; ++tt) {
+        if (!live[tt]) continue;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc[tt][u] = acc[tt][u] / (1.0f + expf(-acc[tt][u]));
+        store8(out + (size_t)(t0 + tt) * channels + c, acc[tt]);
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(THREADS)
 conv_state_update_kernel(const T* __restrict__ x, int ld, int x_off, const int* __restrict__ req_q_start,
@@ -132,6 +225,20 @@ MG_API int mg_causal_conv_silu(const void* x, int ld, int x_off, const float* ta
     const dim3 grid(ceil_div(channels, THREADS), n_tokens), block(THREADS);
     MG_REQUIRE(grid.y <= 65535u * 32768u, "causal_conv: too many tokens");
     cudaStream_t s = (cudaStream_t)stream;
+    if (channels % 8 == 0 && ld % 8 == 0 && x_off % 8 == 0 && state_stride % 4 == 0 && (uintptr_t)x % 16 == 0 &&
+        (uintptr_t)out % 16 == 0 && (uintptr_t)state % 16 == 0 && n_tokens <= 65535) {
+        const bool many = n_tokens > 64;                   // few tokens: one per thread, for more threads
+        const dim3 g(ceil_div(channels / 8, THREADS), many ? ceil_div(n_tokens, 4) : n_tokens);
+#define MG_CONV_VEC(T, TT)                                                                                              \
+    mg_launch(causal_conv_silu_vec_kernel<T, TT>, g, block, 0, s, true, (const T*)x, ld, x_off, taps, bias, token_request, \
+              positions, req_q_start, req_ctx_before, req_state_slot, state, state_stride, (T*)out, channels, n_taps,     \
+              n_requests, n_slots, n_tokens)
+        const cudaError_t e = is_bf16 ? (many ? MG_CONV_VEC(bf16, 4) : MG_CONV_VEC(bf16, 1))
+                                      : (many ? MG_CONV_VEC(float, 4) : MG_CONV_VEC(float, 1));
+#undef MG_CONV_VEC
+        if (e != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "causal_conv: %s", cudaGetErrorString(e));
+        return MG_OK;
+    }
     // (the grid's second dimension takes 65,535 rows: longer steps run in slices)
     for (int t0 = 0; t0 < n_tokens; t0 += 65535) {
         const int nt = n_tokens - t0 < 65535 ? n_tokens - t0 : 65535;
