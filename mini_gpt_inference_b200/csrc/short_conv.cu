@@ -137,7 +137,9 @@ causal_conv_silu_vec_kernel(const T* __restrict__ x, int ld, int x_off, const fl
     for (int tt = 0; tt < TT; ++tt) {
         if (!live[tt]) continue;
 #pragma unroll
-        for (int u = 0; u < 8; ++u) acc[tt][u] = acc[tt][u] / (1.0f + expf(-acc[tt][u]));
+        for (int u = 0; u < 8; ++u)                        // (bfloat16 results: the fast exponential and division are far
+            acc[tt][u] = sizeof(T) == 2 ? __fdividef(acc[tt][u], 1.0f + __expf(-acc[tt][u]))   //  inside their rounding)
+                                        : acc[tt][u] / (1.0f + expf(-acc[tt][u]));
         store8(out + (size_t)(t0 + tt) * channels + c, acc[tt]);
     }
 }
