@@ -72,11 +72,12 @@ head_linear_kernel(const T* __restrict__ x, int x_ld, int x_off, int x_head, con
 }
 
 
-// bfloat16 with many tokens: tiles of 64 tokens x 64 outputs per CTA of four warps on the warp-level tensor cores
+// bfloat16 with many tokens: tiles of 128 tokens x 64 outputs per CTA of four warps (32 tokens a warp, so that a
+// fragment of the head's matrix serves two products) on the warp-level tensor cores
 // (mma.sync m16n8k16, 32-bit accumulation), the sum over i in steps of 64 through shared memory.  A head's matrix is
 // read as it lies: rows that are outputs through ldmatrix, rows that are inputs through ldmatrix.trans.  A token's
 // result depends on its own row only.
-constexpr int MT = 64, MN = 64, MK = 64, MPAD = 8;
+constexpr int MT = 128, MN = 64, MK = 64, MPAD = 8;
 
 __device__ __forceinline__ void hl_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -104,9 +105,11 @@ head_linear_mma_kernel(const bf16* __restrict__ x, int x_ld, int x_off, int x_he
     pdl_wait();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, h = blockIdx.y;
     const int n0 = blockIdx.x * MT, j0 = blockIdx.z * MN;
-    float acc[MN / 8][4];
+    float acc[2][MN / 8][4];
 #pragma unroll
-    for (int n = 0; n < MN / 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+    for (int n = 0; n < MN / 8; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[0][n][e] = acc[1][n][e] = 0.f;
     const bf16* wh = w + (size_t)h * I * J;
     const bf16* xh = x + x_off + (size_t)h * x_head;
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
@@ -130,27 +133,30 @@ head_linear_mma_kernel(const bf16* __restrict__ x, int x_ld, int x_off, int x_he
         __syncthreads();
 #pragma unroll
         for (int kk = 0; kk < MK; kk += 16) {
-            uint32_t a[4];
-            hl_ldsm(a, &xs[warp * 16 + (lane & 15)][kk + (lane >> 4) * 8]);
+            uint32_t a0[4], a1[4];
+            hl_ldsm(a0, &xs[warp * 32 + (lane & 15)][kk + (lane >> 4) * 8]);
+            hl_ldsm(a1, &xs[warp * 32 + 16 + (lane & 15)][kk + (lane >> 4) * 8]);
 #pragma unroll
             for (int n = 0; n < MN / 8; n += 2) {
                 uint32_t b[4];
                 if (rows_are_inputs) hl_ldsm_t(b, &ws[kk + ((lane >> 3) & 1) * 8 + (lane & 7)][n * 8 + (lane >> 4) * 8]);
                 else hl_ldsm(b, &ws[n * 8 + (lane >> 4) * 8 + (lane & 7)][kk + ((lane >> 3) & 1) * 8]);
-                hl_mma(acc[n], a, b[0], b[1]);
-                hl_mma(acc[n + 1], a, b[2], b[3]);
+                hl_mma(acc[0][n], a0, b[0], b[1]);
+                hl_mma(acc[0][n + 1], a0, b[2], b[3]);
+                hl_mma(acc[1][n], a1, b[0], b[1]);
+                hl_mma(acc[1][n + 1], a1, b[2], b[3]);
             }
         }
     }
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        const int n = n0 + warp * 16 + (lane >> 2) + 8 * r;
+    for (int r = 0; r < 4; ++r) {
+        const int n = n0 + warp * 32 + (lane >> 2) + 8 * r;
         if (n >= n_tokens) continue;
 #pragma unroll
         for (int t = 0; t < MN / 8; ++t) {
             const int j = j0 + t * 8 + 2 * (lane & 3);
             if (j >= J) continue;
-            float a = acc[t][2 * r], b = acc[t][2 * r + 1];
+            float a = acc[r >> 1][t][2 * (r & 1)], b = acc[r >> 1][t][2 * (r & 1) + 1];
             if (gate) {
                 const __nv_bfloat162 g = *reinterpret_cast<const __nv_bfloat162*>(gate + (size_t)n * gate_ld + (size_t)h * J + j);
                 a *= 1.0f / (1.0f + expf(-__bfloat162float(g.x)));
