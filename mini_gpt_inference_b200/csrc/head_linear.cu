@@ -10,7 +10,7 @@
 //
 // Tiles of 32 tokens x 64 outputs per CTA, the sum over i in steps of 32 through shared memory, 32-bit
 // accumulation in rising order of i whatever the batch.  x, W, the gate and out are bfloat16 or 32-bit alike.
-// (bfloat16 steps of 16 tokens and more take the tensor-core kernel further down.)
+// (bfloat16 steps take the tensor-core kernel further down where 16-byte loads fit.)
 #include "common.cuh"
 
 namespace {
@@ -77,7 +77,7 @@ head_linear_kernel(const T* __restrict__ x, int x_ld, int x_off, int x_head, con
 // (mma.sync m16n8k16, 32-bit accumulation), the sum over i in steps of 64 through shared memory.  A head's matrix is
 // read as it lies: rows that are outputs through ldmatrix, rows that are inputs through ldmatrix.trans.  A token's
 // result depends on its own row only.
-constexpr int MT = 128, MN = 64, MK = 64, MPAD = 8;
+constexpr int MT = 128, MK = 64, MPAD = 8;
 
 __device__ __forceinline__ void hl_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -95,6 +95,7 @@ __device__ __forceinline__ void hl_ldsm_t(uint32_t (&r)[4], const bf16* p) {
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
 
+template <int MN>            // outputs per CTA: 64, or 16 for steps of few tokens (more CTAs share the heads' matrices)
 __global__ void __launch_bounds__(128)
 head_linear_mma_kernel(const bf16* __restrict__ x, int x_ld, int x_off, int x_head, const bf16* __restrict__ w,
                        int rows_are_inputs, const bf16* __restrict__ gate, int gate_ld, bf16* __restrict__ out, int out_ld,
@@ -124,13 +125,14 @@ head_linear_mma_kernel(const bf16* __restrict__ x, int x_ld, int x_off, int x_he
             const int r = idx >> 3, c = (idx & 7) * 8;
             uint4 v = zero;
             if (rows_are_inputs) {
-                if (i0 + r < I && j0 + c < J) v = *reinterpret_cast<const uint4*>(wh + (size_t)(i0 + r) * J + j0 + c);
+                if (c < MN && i0 + r < I && j0 + c < J) v = *reinterpret_cast<const uint4*>(wh + (size_t)(i0 + r) * J + j0 + c);
             } else {
-                if (j0 + r < J && i0 + c < I) v = *reinterpret_cast<const uint4*>(wh + (size_t)(j0 + r) * I + i0 + c);
+                if (r < MN && j0 + r < J && i0 + c < I) v = *reinterpret_cast<const uint4*>(wh + (size_t)(j0 + r) * I + i0 + c);
             }
             *reinterpret_cast<uint4*>(&ws[r][c]) = v;
         }
         __syncthreads();
+        if (n0 + warp * 32 >= n_tokens) continue;          // a warp without tokens only helps with the loads
 #pragma unroll
         for (int kk = 0; kk < MK; kk += 16) {
             uint32_t a0[4], a1[4];
@@ -187,12 +189,17 @@ MG_API int mg_head_linear(const void* x, int x_ld, int x_off, int x_head, const 
     const bool vectors = I % 8 == 0 && J % 8 == 0 && x_ld % 8 == 0 && x_off % 8 == 0 && x_head % 8 == 0 && out_ld % 2 == 0 &&
                          out_off % 2 == 0 && out_head % 2 == 0 && gate_ld % 2 == 0 && (uintptr_t)x % 16 == 0 &&
                          (uintptr_t)w % 16 == 0 && (uintptr_t)out % 4 == 0 && (uintptr_t)gate % 4 == 0;
-    if (is_bf16 && vectors && n_tokens >= 16) {
-        const dim3 tiles(ceil_div(n_tokens, MT), n_head, ceil_div(J, MN));
+    if (is_bf16 && vectors) {
+        const int mn = n_tokens <= 32 ? 16 : 64;
+        const dim3 tiles(ceil_div(n_tokens, MT), n_head, ceil_div(J, mn));
         MG_REQUIRE(tiles.z <= 65535, "head_linear: too many outputs");
-        const cudaError_t em = mg_launch(head_linear_mma_kernel, tiles, dim3(128), 0, s, true, (const bf16*)x, x_ld, x_off,
-                                         x_head, (const bf16*)w, rows_are_inputs, (const bf16*)gate, gate_ld, (bf16*)out, out_ld,
-                                         out_off, out_head, n_tokens, I, J);
+        const cudaError_t em =
+            mn == 16 ? mg_launch(head_linear_mma_kernel<16>, tiles, dim3(128), 0, s, true, (const bf16*)x, x_ld, x_off, x_head,
+                                 (const bf16*)w, rows_are_inputs, (const bf16*)gate, gate_ld, (bf16*)out, out_ld, out_off, out_head,
+                                 n_tokens, I, J)
+                     : mg_launch(head_linear_mma_kernel<64>, tiles, dim3(128), 0, s, true, (const bf16*)x, x_ld, x_off, x_head,
+                                 (const bf16*)w, rows_are_inputs, (const bf16*)gate, gate_ld, (bf16*)out, out_ld, out_off, out_head,
+                                 n_tokens, I, J);
         if (em != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "head_linear (mma): %s", cudaGetErrorString(em));
         return MG_OK;
     }
