@@ -96,6 +96,44 @@ def config(which: str) -> dict:
     raise KeyError(which)
 
 
+def random_config(rng) -> dict:
+    """A configuration drawn at random: 3 to 8 layers of the three mixer kinds in any order, some without a
+    feed-forward, latent layers that read an earlier one's rows, none to four streams, sizes that are not the
+    fixed cases' (1 to 20 heads, heads of 32 to 128, windows of 17 to 257, latents of 48 to 256, states of 16 to 128)."""
+    width = rng.choice([96, 128, 160, 192, 256, 320])
+    n_layers = rng.randint(3, 8)
+    layers, latent_sources = [], []
+    for i in range(n_layers):
+        kind = rng.choice(["attention", "latent_attention", "mamba2"])
+        mlp = None if rng.random() < 0.3 else _dense(rng.choice([128, 192, 256, 384]))
+        if kind == "attention":
+            kv = rng.choice([1, 2, 3, 4]); heads = kv * rng.choice([1, 2, 3, 4])
+            dim = rng.choice([32, 48, 64, 96, 128]); vdim = rng.choice([32, 64, 128])
+            rot = rng.choice([dim, dim // 2, 16]); rot -= rot % 2
+            layer = _attn(heads, kv, dim, vdim, 1 / math.sqrt(dim), window=rng.choice([17, 64, 100, 140, 200, 257]),
+                             rot=(rot, rng.choice([1e4, 3e5, 1e6])), softcap=rng.choice([15.0, 25.0, 50.0]))
+        elif kind == "latent_attention":
+            heads = rng.choice([2, 4, 6, 8, 12, 16, 20]); dim = rng.choice([32, 64, 128]); vdim = rng.choice([32, 64, 128])
+            if latent_sources and rng.random() < 0.5:
+                src = rng.choice(latent_sources)
+                m = layers[src]["mixer"]
+                layer = _latent(heads, dim, m["rot_dim"], vdim, m["kv_rank"], 1 / math.sqrt(dim + m["rot_dim"]), m["rot"]["base"], kv_from=src)
+            else:
+                rot_dim = rng.choice([16, 32, 64]); rank = rng.choice([48, 64, 96, 128, 192, 256])
+                layer = _latent(heads, dim, rot_dim, vdim, rank, 1 / math.sqrt(dim + rot_dim), rng.choice([1e4, 5e4]))
+                latent_sources.append(i)
+        else:
+            groups = rng.choice([1, 2, 4]); heads = groups * rng.choice([1, 2, 3, 4]); vdim = rng.choice([16, 32, 64])
+            parts = rng.choice([p for p in (1, 2, 4, heads) if (heads * vdim) % p == 0])
+            layer = _mamba(heads, vdim, rng.choice([16, 32, 64, 128]), groups, rng.choice([2, 3, 4]), parts)
+        layers.append({**layer, "mlp": mlp})
+    raw = {"architecture": "Nukodra", "vocab": rng.choice([300, 480, 512, 1000]), "width": width, "layers": layers,
+           "norm": {"eps": rng.choice([1e-5, 1e-6])}}
+    s = rng.choice([None, 1, 2, 3, 4])
+    if s: raw["streams"] = s
+    return raw
+
+
 PAGE_TOKENS = {"A": 8, "B": 16, "C": 4, "D": 16, "E": 8, "F": 4}
 
 

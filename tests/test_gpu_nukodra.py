@@ -399,3 +399,41 @@ def test_one_small_matrix_per_head(dtype, tokens, heads, n_in, n_out):
             lo = 8 + h * (n_out + 4)
             assert torch.allclose(back[:, lo: lo + n_out], want[:, h], atol=tol, rtol=tol)
             assert bool((back[:, lo + n_out: lo + n_out + 4] == 7.0).all())       # nothing written between the heads
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_configurations_drawn_at_random(seed):
+    """Other sizes, head counts, layer orders, windows and constants than the fixed cases: whole prompts, and the
+    same prompt in portions of changing size with its last 40 tokens one by one, in both dtypes."""
+    import random
+
+    from nukodra_cases import random_config
+
+    rng = random.Random(seed)
+    raw = random_config(rng)
+    pt = rng.choice([16, 64])
+    n = rng.choice([150, 333, 420])
+    tokens = tokens_for(raw, n, seed)
+    for dtype in ("float32", "bfloat16"):
+        from mini_gpt_inference_b200.kernels.ops import default_ops
+
+        tensors = random_weights(raw, seed, sharp=2.0 if dtype == "float32" else 1.0, as_bfloat16=dtype == "bfloat16")
+        loaded = load_model(config=NukodraConfig.from_dict(raw), tensors=tensors, dtype=dtype, device="cuda:0")
+        runner = make_runner(loaded, default_ops("cuda:0"), pt, 64, 4)
+        want = plain_logits(raw, tensors, tokens)
+        whole = runner.step([StepEntry("w", tokens, list(range(n)))])
+        runner.finish("w")
+        cuts, at = [], 0
+        while at < n - 40:
+            cuts.append(min(rng.choice([2, 3, 17, 64, 65, 130]), n - 40 - at))
+            at += cuts[-1]
+        cuts += [1] * (n - at)
+        rows, at = [], 0
+        for c in cuts:
+            rows.append(runner.step([StepEntry("c", tokens[at: at + c], list(range(c)))]))
+            at += c
+        runner.finish("c")
+        for what, got in (("whole", whole), ("in portions", torch.cat(rows))):
+            assert_rows_close(got, want, TOL[dtype], f"seed {seed} {dtype} {what}", outliers=0.03 if dtype == "bfloat16" else 0.0)
+        runner.manager.check()
+        assert runner.manager.stats()["allocated_blocks"] == 0
