@@ -2,7 +2,7 @@
 
 __version__ = "0.1.0"
 
-from .config import EngineConfig, FakilornConfig, GPTConfig, NukodraConfig, SamplingParams, ZenedraConfig  # noqa: E402
+from .config import EngineConfig, FakilornConfig, GPTConfig, LunelornConfig, NukodraConfig, SamplingParams, ZenedraConfig  # noqa: E402
 from .engine import LLMEngine, Request, RequestOutput  # noqa: E402
 
-__all__ = ["EngineConfig", "FakilornConfig", "GPTConfig", "NukodraConfig", "SamplingParams", "ZenedraConfig", "LLMEngine", "Request", "RequestOutput"]
+__all__ = ["EngineConfig", "FakilornConfig", "GPTConfig", "LunelornConfig", "NukodraConfig", "SamplingParams", "ZenedraConfig", "LLMEngine", "Request", "RequestOutput"]

@@ -20,7 +20,7 @@ from collections.abc import Sequence
 from dataclasses import dataclass, field
 
 from .page_pool import PagePool, PoolError, SlotPool
-from .spec import FixedStateSpec, PagedKVSpec
+from .spec import FixedStateSpec, PagedKVSpec, PagedKVWithStateSpec
 
 NO_PAGE = -1
 
@@ -76,6 +76,9 @@ class CacheManager:
         for layer, spec in enumerate(layer_specs):
             if spec is None:
                 continue
+            if isinstance(spec, PagedKVWithStateSpec):
+                self.state_layers[layer] = spec.state
+                spec = spec.pages
             if isinstance(spec, FixedStateSpec):
                 self.state_layers[layer] = spec
             elif isinstance(spec, PagedKVSpec):

@@ -58,3 +58,13 @@ class FixedStateSpec:
 
     shape: tuple[int, ...]
     dtype: str = "float32"
+
+
+@dataclass(frozen=True)
+class PagedKVWithStateSpec:
+    """Both at once: keys and values in pages and a tensor of fixed shape in the request's state slot (a layer
+    whose mixer runs an attention and a recurrence side by side).  The pages join the group of layers with an equal
+    ``pages`` spec; the layer's view of the cache carries its ``state`` beside them."""
+
+    pages: PagedKVSpec
+    state: FixedStateSpec

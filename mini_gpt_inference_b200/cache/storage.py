@@ -27,6 +27,7 @@ class PagedKVView:
     window: int | None
     writes: bool
     values_in_keys: bool = False   # v_pages is k_pages: a token's values are the first features of its key row
+    state: torch.Tensor | None = None   # [slot, *shape], where the layer also keeps a tensor per request
 
 
 @dataclass
@@ -59,7 +60,8 @@ class CacheStorage:
             g = m.group_of_layer[cache_layer]
             idx = m.groups[g].layers.index(cache_layer)
             return PagedKVView(self.k[g][idx], self.v[g][idx], g, m.groups[g].page_tokens,
-                               m.groups[g].spec.window, writes, m.groups[g].spec.values_in_keys)
+                               m.groups[g].spec.window, writes, m.groups[g].spec.values_in_keys,
+                               self.state.get(cache_layer))
         if cache_layer in self.state:
             return StateView(self.state[cache_layer], writes)
         return None

@@ -86,4 +86,4 @@ def load_config(model_dir) -> tuple[ModelFamily, Any]:
 
 def _ensure_builtin_models() -> None:
     # Importing the module registers the family; done lazily to avoid an import cycle.
-    from ..models import fakilorn, minigpt, nukodra, zenedra  # noqa: F401
+    from ..models import fakilorn, lunelorn, minigpt, nukodra, zenedra  # noqa: F401

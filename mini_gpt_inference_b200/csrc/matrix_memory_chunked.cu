@@ -25,6 +25,12 @@
 // them.  What differs is read where the rows are loaded (`ssd`): the logarithm of the decay is -exp(A_h) dt_t with
 // dt_t = softplus(gates[t, h]), the values enter the memory as dt_t x_t, queries are not scaled, q and k (the C and
 // B of the state-space form) are shared by `qk_group` neighbouring heads, and D_h x_t is added to the output.
+//
+// Retention (`form` 3) is the same with one fixed decay a_h per head: the logarithm of the decay is log(a_h) at every
+// token, keys are scaled by head_dim^(-1/2) and queries are not.  The wkv form (`form` 4; RWKV-6 time mixing) has a
+// decay exp(-exp(z_t)) per key channel like gated linear attention, but reads BEFORE it updates: o_t = (S_(t-1) +
+// diag(u) k_t v_t^T)^T q_t.  So in kernel 3 the query of token t sees the state and the chunk's earlier tokens through
+// b_(t-1) instead of b_t (b_(-1) = 0), and its own token through the bonus u alone: A_tt = sum_d q_t[d] u[d] k_t[d].
 #include <math.h>
 
 #include "common.cuh"
@@ -41,7 +47,7 @@ __device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - l
 __device__ __forceinline__ float softplus(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
 
 struct ChunkParams {
-    const void* proj; int ld, q_off, k_off, v_off;
+    const void* proj; int ld; long long q_off, k_off, v_off;
     const float* gates; int gates_ld;
     const int* chunks;            // [n_chunks, 4]: request, first row, tokens, unused
     const int* req_chunks;        // [n_requests, 2]: first chunk, number of chunks
@@ -54,7 +60,8 @@ struct ChunkParams {
     int n_chunks, n_requests, n_tokens, n_head, d, dv, L, n_slots;
     float constant;
     int ssd, qk_group;            // the state-space form: q and k columns of head h / qk_group
-    const float* head_consts;     // ssd: [2 H]: A_h, then D_h
+    int form;                     // 0: gated linear attention, 2: state-space, 3: retention, 4: wkv
+    const float* head_consts;     // ssd: [2 H]: A_h, then D_h;  retention: [H] decays;  wkv: [H, D] bonus
 };
 
 // ---- kernel 1 ----------------------------------------------------------------------------------------
@@ -77,11 +84,14 @@ __global__ void __launch_bounds__(THREADS) chunk_local_kernel(const ChunkParams 
         // keys as the chunk's end sees them, all at once again
         const float inv_tau = p.ssd ? 0.f : 1.0f / p.constant;
         const float rate = p.ssd ? expf(p.head_consts[h]) : 0.f;
+        const float fixed_la = p.form == 3 ? fmaxf(logf(p.head_consts[h]), -1.0e4f) : 0.f;   // (a decay of 0 stays finite)
         for (int idx = tid; idx < L * D; idx += THREADS) {
             const int j = idx / D, d = idx - j * D;
             float la = 0.f;
             if (j < count)
                 la = p.ssd ? -rate * softplus(p.gates[(size_t)(row0 + j) * p.gates_ld + h])
+                   : p.form == 3 ? fixed_la
+                   : p.form == 4 ? -expf(p.gates[(size_t)(row0 + j) * p.gates_ld + (size_t)h * D + d])
                            : log_sigmoid(p.gates[(size_t)(row0 + j) * p.gates_ld + (size_t)h * D + d]) * inv_tau;
             fc[j * (D + 1) + d] = la;
         }
@@ -101,6 +111,7 @@ __global__ void __launch_bounds__(THREADS) chunk_local_kernel(const ChunkParams 
             if (j < count) {
                 p.cum[((size_t)(row0 + j) * p.n_head + h) * D + d] = b;
                 kv = to_float(proj[(size_t)(row0 + j) * p.ld + p.k_off + (size_t)(h / p.qk_group) * D + d]) * expf(b_end - b);
+                if (p.form == 3) kv *= 1.0f / sqrtf((float)D);
             }
             kt[j * (D + 1) + d] = kv;
         }
@@ -241,7 +252,9 @@ __global__ void __launch_bounds__(THREADS) chunk_output_kernel(const ChunkParams
     if (!MG_GUARDED(matrix_memory_chunked, MG_GUARD_ROW, row0 + count - 1, p.n_tokens) || count <= 0 || count > L) return;
     const T* proj = reinterpret_cast<const T*>(p.proj);
     const bool ssd = !MLSTM && p.ssd;
-    const float q_scale = ssd ? 1.0f : 1.0f / sqrtf((float)D);
+    const bool wkv = !MLSTM && p.form == 4;
+    const float q_scale = (ssd || (!MLSTM && p.form >= 3)) ? 1.0f : 1.0f / sqrtf((float)D);
+    const float k_scale = (!MLSTM && p.form == 3) ? 1.0f / sqrtf((float)D) : 1.0f;
     const int hq = h / p.qk_group;
     for (int idx = tid; idx < L * D; idx += THREADS) {
         const int j = idx / D, d = idx - j * D;
@@ -249,7 +262,7 @@ __global__ void __launch_bounds__(THREADS) chunk_output_kernel(const ChunkParams
         if (j < count) {
             const T* row = proj + (size_t)(row0 + j) * p.ld + (size_t)hq * D + d;
             qv = to_float(row[p.q_off]) * q_scale;
-            kv = to_float(row[p.k_off]);
+            kv = to_float(row[p.k_off]) * k_scale;
             if (!MLSTM) bv = p.cum[((size_t)(row0 + j) * p.n_head + h) * D + d];
         }
         qs[j * (D + 1) + d] = qv;
@@ -299,6 +312,15 @@ __global__ void __launch_bounds__(THREADS) chunk_output_kernel(const ChunkParams
             if (MLSTM) {
                 for (int d = 0; d < D; ++d) a = fmaf(qr[d], kr[d], a);
                 a *= __expf(bs[t] - bs[j] + bs[L + j] - bs[2 * L + t]);
+            } else if (wkv) {
+                if (j == t) {                                        // the token itself: the bonus in place of a decay
+                    const float* u = p.head_consts + (size_t)h * D;
+                    for (int d = 0; d < D; ++d) a = fmaf(qr[d] * kr[d], u[d], a);
+                } else {                                             // the state before token t: decays up to t - 1
+                    const float* bt = bs + (t - 1) * (D + 1);
+                    const float* bj = bs + j * (D + 1);
+                    for (int d = 0; d < D; ++d) a = fmaf(qr[d] * kr[d], __expf(bt[d] - bj[d]), a);
+                }
             } else {
                 const float* bt = bs + t * (D + 1);
                 const float* bj = bs + j * (D + 1);
@@ -311,7 +333,8 @@ __global__ void __launch_bounds__(THREADS) chunk_output_kernel(const ChunkParams
     // the queries as the state before the chunk sees them
     for (int idx = tid; idx < L * D; idx += THREADS) {
         const int t = idx / D, d = idx - t * D;
-        const float f = MLSTM ? __expf(bs[t] + m_prev - bs[2 * L + t]) : __expf(bs[t * (D + 1) + d]);
+        const float f = MLSTM ? __expf(bs[t] + m_prev - bs[2 * L + t])
+                      : wkv ? (t > 0 ? __expf(bs[(t - 1) * (D + 1) + d]) : 1.f) : __expf(bs[t * (D + 1) + d]);
         qs[t * (D + 1) + d] *= f;
     }
     __syncthreads();
@@ -416,27 +439,31 @@ MG_API int mg_matrix_memory_chunk_tokens(int head_dim, int v_dim, int mlstm) {
 // [n_chunks, n_head, v_dim + mlstm, head_dim] floats; chunk_meta: [n_chunks, n_head, 4] floats (mlstm; else null).
 // qk_group > 0 with head_consts ([A_0 .. A_(H-1), D_0 .. D_(H-1)], 32-bit): the state-space form (not with mlstm);
 // gates then hold one step size per head before its softplus, and `state` points at the memories of slot 0.
-MG_API int mg_matrix_memory_chunked(const void* proj, int ld, int q_off, int k_off, int v_off, const float* gates,
+// form 3 (retention: head_consts = [H] decays, no gates) and 4 (wkv: head_consts = [H, D] bonus, gates = the decays'
+// pre-activations [tokens, H * D]); 0: as said above.  Offsets beyond a row name planes, as in mg_matrix_memory_scan.
+MG_API int mg_matrix_memory_chunked(const void* proj, int ld, long long q_off, long long k_off, long long v_off, const float* gates,
                                     int gates_ld, const int* chunks, const int* req_chunks, const int* req_ctx_before,
                                     const int* req_state_slot, float* state, long long state_stride, float* cum,
                                     float* chunk_state, float* chunk_meta, float* out, float* aux, int n_chunks,
                                     int chunk_tokens, int n_requests, int n_tokens, int n_head, int head_dim, int v_dim,
                                     float constant, int mlstm, int n_slots, int is_bf16, int qk_group,
-                                    const float* head_consts, void* stream) {
+                                    const float* head_consts, int form, void* stream) {
     if (n_requests == 0 || n_tokens == 0 || n_chunks == 0) return MG_OK;
     MG_REQUIRE(n_requests > 0 && n_tokens > 0 && n_chunks > 0 && n_head > 0 && head_dim > 0 && v_dim > 0 && n_slots > 0,
                "matrix memory (chunks): bad sizes");
     MG_REQUIRE(n_head <= 65535 && n_requests <= 65535, "matrix memory (chunks): too many heads or requests");
-    const bool ssd = head_consts != nullptr;
-    MG_REQUIRE(ssd || constant > 0.f, "matrix memory (chunks): tau and the gates' cap must be positive");
+    MG_REQUIRE(form == 0 || ((form == 3 || form == 4) && !mlstm && head_consts != nullptr), "matrix memory (chunks): form %d", form);
+    const bool ssd = head_consts != nullptr && form == 0;
+    MG_REQUIRE(ssd || form != 0 || constant > 0.f, "matrix memory (chunks): tau and the gates' cap must be positive");
     MG_REQUIRE(!ssd || (!mlstm && qk_group > 0 && n_head % qk_group == 0), "matrix memory (chunks): %d heads do not form groups of %d", n_head, qk_group);
     if (!ssd) qk_group = 1;
     const int qk_heads = n_head / qk_group;
     const int cols = v_dim + (mlstm ? 1 : 0);
     MG_REQUIRE(state_stride >= (long long)n_head * cols * head_dim + (mlstm ? n_head : 0), "matrix memory (chunks): the state slots are too small");
-    MG_REQUIRE(q_off >= 0 && k_off >= 0 && v_off >= 0 && q_off + qk_heads * head_dim <= ld && k_off + qk_heads * head_dim <= ld &&
-                   v_off + n_head * v_dim <= ld, "matrix memory (chunks): heads outside the rows");
-    MG_REQUIRE(gates_ld >= (mlstm ? 2 * n_head : ssd ? n_head : n_head * head_dim), "matrix memory (chunks): the gates' rows are too short");
+    MG_REQUIRE(q_off >= 0 && k_off >= 0 && v_off >= 0 && q_off % ld + qk_heads * head_dim <= ld && k_off % ld + qk_heads * head_dim <= ld &&
+                   v_off % ld + n_head * v_dim <= ld, "matrix memory (chunks): heads outside the rows");
+    MG_REQUIRE(form == 3 || (gates != nullptr && gates_ld >= (mlstm ? 2 * n_head : ssd ? n_head : n_head * head_dim)),
+               "matrix memory (chunks): the gates' rows are too short");
     MG_REQUIRE(cum && chunk_state && (!mlstm || (chunk_meta && aux)), "matrix memory (chunks): scratch is missing");
     MG_REQUIRE((chunk_tokens == 32 || chunk_tokens == 64) && chunk_tokens <= mg_matrix_memory_chunk_tokens(head_dim, v_dim, mlstm),
                "matrix memory (chunks): chunks of %d tokens do not fit heads of %d and %d", chunk_tokens, head_dim, v_dim);
@@ -446,7 +473,7 @@ MG_API int mg_matrix_memory_chunked(const void* proj, int ld, int q_off, int k_o
     p.state = state; p.state_stride = state_stride; p.cum = cum; p.chunk_state = chunk_state; p.chunk_meta = chunk_meta;
     p.out = out; p.aux = aux; p.n_chunks = n_chunks; p.n_requests = n_requests; p.n_tokens = n_tokens; p.n_head = n_head;
     p.d = head_dim; p.dv = v_dim; p.L = chunk_tokens; p.n_slots = n_slots; p.constant = constant;
-    p.ssd = ssd ? 1 : 0; p.qk_group = qk_group; p.head_consts = head_consts;
+    p.ssd = ssd ? 1 : 0; p.qk_group = qk_group; p.head_consts = head_consts; p.form = ssd ? 2 : form;
     cudaStream_t s = (cudaStream_t)stream;
     if (is_bf16) return mlstm ? run_chunked<bf16, true>(p, s) : run_chunked<bf16, false>(p, s);
     return mlstm ? run_chunked<float, true>(p, s) : run_chunked<float, false>(p, s);

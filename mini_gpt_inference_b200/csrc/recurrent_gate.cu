@@ -1,0 +1,146 @@
+// A gated recurrence whose gates read only the current token (minGRU), element by element, and the blend of a token's
+// input with the input of the token before it that RWKV-style mixers feed their projections with.
+//
+// gated_recurrence: rows [ ... z (W) ... u (W) ... g (W) ... ] of 32-bit pre-activations (biases included), per
+// request r and channel c, over the request's tokens t in order:
+//   s <- (1 - sigmoid(z_t)) s + sigmoid(z_t) cand(u_t),   cand(u) = u + 1/2 for u >= 0, sigmoid(u) below,
+//   out_t = s * silu(g_t)
+// s lives in the request's state slot in 32-bit and starts at zero when the request has nothing in the cache.  One
+// thread owns a channel; a token is one multiply-add on the chain, everything else (the loads of eight tokens at a
+// time, the logistic functions) does not wait for the state.  The order of the sums is the tokens' order whatever
+// the cut into steps.
+//
+// token_shift_mix: with h_t a token's input and h_(t-1) the input of the token before it in its sequence (zeros for a
+// sequence's first token; for a step's first token of a request it is read from the request's state slot),
+//   out[s][t] = h_t + (h_(t-1) - h_t) * mu[s]        for s = 0 .. n_mixes - 1
+// conv_state_update of short_conv.cu with two taps leaves a step's last input in the slot afterwards.
+#include <math.h>
+
+#include "common.cuh"
+
+MG_GUARD_DECLARE(recurrent_gate)
+
+namespace {
+
+constexpr int THREADS = 128;
+constexpr int AHEAD = 8;          // tokens whose rows are loaded before the chain runs over them
+
+__device__ __forceinline__ float sigmoidf(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS)
+gated_recurrence_kernel(const float* __restrict__ pre, int ld, int z_off, int u_off, int g_off,
+                        const int* __restrict__ req_q_start, const int* __restrict__ req_q_len,
+                        const int* __restrict__ req_ctx_before, const int* __restrict__ req_state_slot,
+                        float* __restrict__ state, long long state_stride, T* __restrict__ out, int width, int n_slots,
+                        int n_tokens) {
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.y, c = blockIdx.x * THREADS + threadIdx.x;
+    const int q_len = req_q_len[r];
+    if (q_len <= 0 || c >= width) return;                      // a padding row of a fixed-size batch
+    const int start = req_q_start[r];
+    int slot = req_state_slot[r];
+    if (!MG_GUARDED(recurrent_gate, MG_GUARD_ROW, slot, n_slots) ||
+        !MG_GUARDED(recurrent_gate, MG_GUARD_ROW, start + q_len - 1, n_tokens))
+        return;
+    float* s_ptr = state + (size_t)slot * state_stride + c;
+    float s = req_ctx_before[r] == 0 ? 0.f : *s_ptr;
+    for (int t0 = 0; t0 < q_len; t0 += AHEAD) {
+        float zv[AHEAD], uv[AHEAD], gv[AHEAD];
+#pragma unroll
+        for (int i = 0; i < AHEAD; ++i) {
+            const bool live = t0 + i < q_len;
+            const float* row = pre + (size_t)(start + t0 + (live ? i : 0)) * ld + c;
+            zv[i] = row[z_off];
+            uv[i] = row[u_off];
+            gv[i] = row[g_off];
+        }
+#pragma unroll
+        for (int i = 0; i < AHEAD; ++i) {
+            if (t0 + i >= q_len) break;
+            const float z = sigmoidf(zv[i]);
+            const float cand = uv[i] >= 0.f ? uv[i] + 0.5f : sigmoidf(uv[i]);
+            s = fmaf(z, cand - s, s);                          // (1 - z) s + z cand
+            out[(size_t)(start + t0 + i) * width + c] = from_float<T>(s * gv[i] * sigmoidf(gv[i]));
+        }
+    }
+    *s_ptr = s;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS)
+token_shift_mix_kernel(const T* __restrict__ x, const float* __restrict__ mu, const int* __restrict__ token_request,
+                       const int* __restrict__ positions, const int* __restrict__ req_q_start,
+                       const int* __restrict__ req_ctx_before, const int* __restrict__ req_state_slot,
+                       const float* __restrict__ state, long long state_stride, T* __restrict__ out, int width,
+                       int n_mixes, int n_tokens, int n_requests, int n_slots) {
+    pdl_trigger();
+    pdl_wait();
+    const int token = blockIdx.x, c = blockIdx.y * THREADS + threadIdx.x;
+    if (c >= width) return;
+    const size_t plane = (size_t)n_tokens * width, at = (size_t)token * width + c;
+    if (positions[token] < 0) {                                // padding: nothing is read for it
+        for (int s = 0; s < n_mixes; ++s) out[s * plane + at] = from_float<T>(0.f);
+        return;
+    }
+    int r = token_request[token];
+    if (!MG_GUARDED(recurrent_gate, MG_GUARD_REQUEST, r, n_requests)) return;
+    int slot = req_state_slot[r];
+    if (!MG_GUARDED(recurrent_gate, MG_GUARD_ROW, slot, n_slots)) return;
+    const float cur = to_float(x[at]);
+    float before;
+    if (token > req_q_start[r]) before = to_float(x[at - width]);
+    else before = req_ctx_before[r] == 0 ? 0.f : state[(size_t)slot * state_stride + c];
+    const float diff = before - cur;
+    for (int s = 0; s < n_mixes; ++s) out[s * plane + at] = from_float<T>(fmaf(diff, mu[(size_t)s * width + c], cur));
+}
+
+}  // namespace
+
+// pre: [n_tokens, ld] 32-bit rows holding z, u and g (width numbers each) at the three column offsets; req_*:
+// [n_requests] first row, tokens, tokens already in the cache, state slot; state: 32-bit, `state_stride` numbers
+// a slot, of which the first `width` (from `state`) are this recurrence's; out: [n_tokens, width].
+MG_API int mg_gated_recurrence(const float* pre, int ld, int z_off, int u_off, int g_off, const int* req_q_start,
+                               const int* req_q_len, const int* req_ctx_before, const int* req_state_slot, float* state,
+                               long long state_stride, void* out, int n_requests, int n_tokens, int width, int n_slots,
+                               int out_bf16, void* stream) {
+    if (n_requests == 0 || n_tokens == 0) return MG_OK;
+    MG_REQUIRE(n_requests > 0 && n_requests <= 65535 && n_tokens > 0 && width > 0 && n_slots > 0 && state_stride >= width,
+               "gated recurrence: bad sizes");
+    MG_REQUIRE(z_off >= 0 && u_off >= 0 && g_off >= 0 && z_off + width <= ld && u_off + width <= ld && g_off + width <= ld,
+               "gated recurrence: columns outside the rows");
+    const dim3 grid(ceil_div(width, THREADS), n_requests);
+    cudaStream_t s = (cudaStream_t)stream;
+    const cudaError_t e =
+        out_bf16 ? mg_launch(gated_recurrence_kernel<bf16>, grid, dim3(THREADS), 0, s, true, pre, ld, z_off, u_off, g_off,
+                             req_q_start, req_q_len, req_ctx_before, req_state_slot, state, state_stride, (bf16*)out, width,
+                             n_slots, n_tokens)
+                 : mg_launch(gated_recurrence_kernel<float>, grid, dim3(THREADS), 0, s, true, pre, ld, z_off, u_off, g_off,
+                             req_q_start, req_q_len, req_ctx_before, req_state_slot, state, state_stride, (float*)out, width,
+                             n_slots, n_tokens);
+    if (e != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "gated recurrence: %s", cudaGetErrorString(e));
+    return MG_OK;
+}
+
+// x: [n_tokens, width] (bfloat16 if is_bf16 else 32-bit); mu: [n_mixes, width] 32-bit; state: 32-bit slots whose
+// first `width` numbers are the request's last input; out: [n_mixes, n_tokens, width] in x's type.
+MG_API int mg_token_shift_mix(const void* x, const float* mu, const int* token_request, const int* positions,
+                              const int* req_q_start, const int* req_ctx_before, const int* req_state_slot,
+                              const float* state, long long state_stride, void* out, int n_tokens, int width, int n_mixes,
+                              int n_requests, int n_slots, int is_bf16, void* stream) {
+    if (n_tokens == 0) return MG_OK;
+    MG_REQUIRE(n_tokens > 0 && width > 0 && width <= 65535 * THREADS && n_mixes > 0 && n_slots > 0 && state_stride >= width,
+               "token shift: bad sizes");
+    const dim3 grid(n_tokens, ceil_div(width, THREADS));
+    cudaStream_t s = (cudaStream_t)stream;
+    const cudaError_t e =
+        is_bf16 ? mg_launch(token_shift_mix_kernel<bf16>, grid, dim3(THREADS), 0, s, true, (const bf16*)x, mu, token_request,
+                            positions, req_q_start, req_ctx_before, req_state_slot, state, state_stride, (bf16*)out, width,
+                            n_mixes, n_tokens, n_requests, n_slots)
+                : mg_launch(token_shift_mix_kernel<float>, grid, dim3(THREADS), 0, s, true, (const float*)x, mu,
+                            token_request, positions, req_q_start, req_ctx_before, req_state_slot, state, state_stride,
+                            (float*)out, width, n_mixes, n_tokens, n_requests, n_slots);
+    if (e != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "token shift: %s", cudaGetErrorString(e));
+    return MG_OK;
+}

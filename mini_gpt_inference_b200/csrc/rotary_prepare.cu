@@ -6,7 +6,13 @@
 //     and one over all key features, each with a gain of that whole size;
 //   * the first R features of every query and key head turn: feature i pairs with i + R/2,
 //     (u, v) -> (u cos a - v sin a, v cos a + u sin a), a = position * f_i, f_i given as a table of R/2 numbers;
+//   * optionally every value head is divided by its root mean square (no gain), and optionally all its Dv features
+//     turn with the position like a key head's would (feature m pairs with m + Dv/2, a = position * g_m, g_m given as
+//     a second table of Dv/2 numbers): what attention then sums are values in the frame of their own positions;
 //   * queries are written back in place, keys and values go to their cache rows.
+//
+// `rotate_heads`: rows [H x Dv] (the heads an attention over such values returns) turned by MINUS the token's own
+// position, in place: the sum over the values comes back into the frame of the query.
 //
 // `latent_prepare`: rows [ ... q (H x (D + R)) ... low (C + R) ... ] of an attention whose keys and values are
 // made from one small latent per token:
@@ -56,7 +62,8 @@ qk_norm_rotary_kernel(T* __restrict__ proj, int ld, int n_head, int n_kv_head, i
                       int k_off, int v_off, int norm, float eps, const float* __restrict__ q_gain,
                       const float* __restrict__ k_gain, int rot, const float* __restrict__ freq,
                       const int* __restrict__ positions, const int* __restrict__ slots, T* __restrict__ k_pages,
-                      T* __restrict__ v_pages, int page_tokens, int num_pages) {
+                      T* __restrict__ v_pages, int page_tokens, int num_pages, int v_norm, float v_eps,
+                      const float* __restrict__ v_freq) {
     extern __shared__ float smem[];                        // [H*D] q, [G*D] k, [rot] cos/sin pairs
     __shared__ float red[THREADS / 32];
     pdl_trigger();
@@ -107,9 +114,60 @@ qk_norm_rotary_kernel(T* __restrict__ proj, int ld, int n_head, int n_kv_head, i
         k_pages[(((size_t)page * n_kv_head + h) * page_tokens + within) * head_dim + d] =
             from_float<T>(turned(ks + h * head_dim, k_gain ? k_gain + h * head_dim : nullptr, rk, d, rot, cs));
     }
-    for (int i = tid; i < n_kv_head * v_dim; i += THREADS) {
-        const int h = i / v_dim, d = i - h * v_dim;
-        v_pages[(((size_t)page * n_kv_head + h) * page_tokens + within) * v_dim + d] = row[v_off + i];
+    if (!v_norm && v_freq == nullptr) {
+        for (int i = tid; i < n_kv_head * v_dim; i += THREADS) {
+            const int h = i / v_dim, d = i - h * v_dim;
+            v_pages[(((size_t)page * n_kv_head + h) * page_tokens + within) * v_dim + d] = row[v_off + i];
+        }
+        return;
+    }
+    // a warp takes a value head at a time: its root mean square, then the turn of all its features
+    const int warp = tid >> 5, lane = tid & 31, half = v_dim >> 1;
+    for (int h = warp; h < n_kv_head; h += THREADS / 32) {
+        const T* src = row + v_off + (size_t)h * v_dim;
+        T* dst = v_pages + (((size_t)page * n_kv_head + h) * page_tokens + within) * v_dim;
+        float r = 1.f;
+        if (v_norm) {
+            float sq = 0.f;
+            for (int d = lane; d < v_dim; d += 32) {
+                const float x = to_float(src[d]);
+                sq = fmaf(x, x, sq);
+            }
+            r = 1.0f / sqrtf(warp_sum(sq) / (float)v_dim + v_eps);
+        }
+        if (v_freq == nullptr) {
+            for (int d = lane; d < v_dim; d += 32) dst[d] = from_float<T>(to_float(src[d]) * r);
+            continue;
+        }
+        for (int m = lane; m < half; m += 32) {
+            float sn, cs2;
+            sincosf(__fmul_rn((float)pos, v_freq[m]), &sn, &cs2);
+            const float u = to_float(src[m]) * r, v = to_float(src[m + half]) * r;
+            dst[m] = from_float<T>(u * cs2 - v * sn);
+            dst[m + half] = from_float<T>(v * cs2 + u * sn);
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS)
+rotate_heads_kernel(T* __restrict__ x, int n_head, int v_dim, const float* __restrict__ freq,
+                    const int* __restrict__ positions, float sign) {
+    pdl_trigger();
+    pdl_wait();
+    const int token = blockIdx.x, half = v_dim >> 1;
+    const int pos = positions[token];
+    if (pos < 0) return;
+    T* row = x + (size_t)token * n_head * v_dim;
+    for (int i = threadIdx.x; i < n_head * half; i += THREADS) {
+        const int h = i / half, m = i - h * half;
+        float sn, cs;
+        sincosf(__fmul_rn((float)pos, freq[m]), &sn, &cs);
+        sn *= sign;
+        T* head = row + (size_t)h * v_dim;
+        const float u = to_float(head[m]), v = to_float(head[m + half]);
+        head[m] = from_float<T>(u * cs - v * sn);
+        head[m + half] = from_float<T>(v * cs + u * sn);
     }
 }
 
@@ -187,8 +245,10 @@ latent_prepare_kernel(const T* __restrict__ proj, int ld, int n_head, int q_off,
 MG_API int mg_qk_norm_rotary(void* proj, int ld, int n_tokens, int n_head, int n_kv_head, int head_dim, int v_dim, int q_off,
                              int k_off, int v_off, int norm, float eps, const float* q_gain, const float* k_gain, int rot,
                              const float* freq, const int* positions, const int* slots, void* k_pages, void* v_pages,
-                             int page_tokens, int num_pages, int is_bf16, void* stream) {
+                             int page_tokens, int num_pages, int is_bf16, int v_norm, float v_eps, const float* v_freq,
+                             void* stream) {
     if (n_tokens == 0) return MG_OK;
+    MG_REQUIRE(v_freq == nullptr || v_dim % 2 == 0, "qk_norm_rotary: value heads of %d features do not turn in pairs", v_dim);
     MG_REQUIRE(n_tokens > 0 && n_head > 0 && n_kv_head > 0 && head_dim > 0 && v_dim > 0 && positions != nullptr,
                "qk_norm_rotary: bad sizes");
     MG_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= head_dim && (rot == 0 || freq != nullptr),
@@ -207,15 +267,30 @@ MG_API int mg_qk_norm_rotary(void* proj, int ld, int n_tokens, int n_head, int n
         if (e == cudaSuccess)
             e = mg_launch(qk_norm_rotary_kernel<bf16>, dim3(n_tokens), dim3(THREADS), smem, s, true, (bf16*)proj, ld, n_head,
                           n_kv_head, head_dim, v_dim, q_off, k_off, v_off, norm, eps, q_gain, k_gain, rot, freq, positions,
-                          slots, (bf16*)k_pages, (bf16*)v_pages, page_tokens, num_pages);
+                          slots, (bf16*)k_pages, (bf16*)v_pages, page_tokens, num_pages, v_norm, v_eps, v_freq);
     } else {
         e = smem > 48 * 1024 ? cudaFuncSetAttribute(qk_norm_rotary_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) : cudaSuccess;
         if (e == cudaSuccess)
             e = mg_launch(qk_norm_rotary_kernel<float>, dim3(n_tokens), dim3(THREADS), smem, s, true, (float*)proj, ld, n_head,
                           n_kv_head, head_dim, v_dim, q_off, k_off, v_off, norm, eps, q_gain, k_gain, rot, freq, positions,
-                          slots, (float*)k_pages, (float*)v_pages, page_tokens, num_pages);
+                          slots, (float*)k_pages, (float*)v_pages, page_tokens, num_pages, v_norm, v_eps, v_freq);
     }
     if (e != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "qk_norm_rotary: %s", cudaGetErrorString(e));
+    return MG_OK;
+}
+
+// x: [n_tokens, n_head * v_dim], in place; freq: [v_dim / 2] 32-bit; sign: -1 turns back, +1 forward.
+MG_API int mg_rotate_heads(void* x, int n_tokens, int n_head, int v_dim, const float* freq, const int* positions,
+                           float sign, int is_bf16, void* stream) {
+    if (n_tokens == 0) return MG_OK;
+    MG_REQUIRE(n_tokens > 0 && n_head > 0 && v_dim > 0 && v_dim % 2 == 0 && freq && positions, "rotate_heads: bad sizes");
+    cudaStream_t s = (cudaStream_t)stream;
+    const cudaError_t e =
+        is_bf16 ? mg_launch(rotate_heads_kernel<bf16>, dim3(n_tokens), dim3(THREADS), 0, s, true, (bf16*)x, n_head, v_dim,
+                            freq, positions, sign)
+                : mg_launch(rotate_heads_kernel<float>, dim3(n_tokens), dim3(THREADS), 0, s, true, (float*)x, n_head, v_dim,
+                            freq, positions, sign);
+    if (e != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "rotate_heads: %s", cudaGetErrorString(e));
     return MG_OK;
 }
 

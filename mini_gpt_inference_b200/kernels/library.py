@@ -29,7 +29,17 @@ _SIGNATURES = {
     "mg_streams_read": [_P, _P, _P, _P, _I, ctypes.c_longlong, _P],
     "mg_streams_write": [_P, _P, _P, _P, _P, _P, _P, _I, ctypes.c_longlong, _P],
     "mg_streams_spread": [_P, _P, _I, ctypes.c_longlong, _P],
-    "mg_qk_norm_rotary": [_P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P],
+    "mg_qk_norm_rotary": [_P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I,
+                          _I, _F, _P, _P],
+    "mg_rotate_heads": [_P, _I, _I, _I, _P, _P, _F, _I, _P],
+    "mg_gated_recurrence": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, ctypes.c_longlong, _P, _I, _I, _I, _I, _I, _P],
+    "mg_token_shift_mix": [_P, _P, _P, _P, _P, _P, _P, _P, ctypes.c_longlong, _P, _I, _I, _I, _I, _I, _I, _P],
+    "mg_rmsnorm_add": [_P, _P, _F, _P, _F, _P, _I, _I, _F, _F, _P],
+    "mg_add_rows": [_P, _P, _P, ctypes.c_longlong, _I, _P],
+    "mg_scaled_sum": [_P, _P, _F, _P, _F, ctypes.c_longlong, _P],
+    "mg_softcap": [_P, ctypes.c_longlong, _F, _P],
+    "mg_cast_rows": [_P, _P, ctypes.c_longlong, _I, _I, _P],
+    "mg_token_gate": [_P, _P, _P, _P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _I, _I, _P],
     "mg_latent_prepare": [_P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _F, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "mg_head_linear": [_P, _I, _I, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "mg_causal_conv_silu": [_P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, ctypes.c_longlong, _P, _I, _I, _I, _I, _I, _I, _P],
@@ -39,10 +49,10 @@ _SIGNATURES = {
                        _I, _I, _P],
     "mg_rmsnorm": [_P, _P, _P, _I, _I, _F, _F, _I, _P],
     "mg_concat_cast": [_P, _P, _P, _I, _I, _I, _P],
-    "mg_matrix_memory_scan": [_P, _I, _I, _I, _I, _P, _I, _P, _P, _P, _P, _P, ctypes.c_longlong, _P, _P, _I, _I, _I, _I,
+    "mg_matrix_memory_scan": [_P, _I, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong, _P, _I, _P, _P, _P, _P, _P, ctypes.c_longlong, _P, _P, _I, _I, _I, _I,
                               _I, _F, _I, _I, _I, _I, _P, _P],
-    "mg_matrix_memory_chunked": [_P, _I, _I, _I, _I, _P, _I, _P, _P, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _P, _P, _I,
-                                 _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P, _P],
+    "mg_matrix_memory_chunked": [_P, _I, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong, _P, _I, _P, _P, _P, _P, _P,
+                                 ctypes.c_longlong, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P, _I, _P],
     "mg_matrix_memory_chunk_tokens": [_I, _I, _I],
     "mg_head_norm_gate": [_P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _F, _I, _I, _I, _P],
     "mg_moe_route_scored": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
@@ -92,7 +102,7 @@ _SIGNATURES = {
 # exported readers of the kernel files' index guards: mg_<name>_index_fault(long long[4])
 GUARDED_FILES = ("elementwise", "linear_skinny", "linear_stream", "linear_wide", "linear_cluster", "linear_tc",
                  "attention_generic", "attention_split", "attention_prefill", "head_prepare", "moe", "attention_mma", "matrix_memory", "matrix_memory_chunked",
-                 "rotary_prepare", "short_conv")
+                 "rotary_prepare", "short_conv", "recurrent_gate", "residual_norm")
 for _name in GUARDED_FILES:
     _SIGNATURES[f"mg_{_name}_index_fault"] = [_P]
 GUARD_CODES = {1: "token id", 2: "position", 3: "cache row", 4: "page", 5: "request", 6: "row", 7: "token source"}

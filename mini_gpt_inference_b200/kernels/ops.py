@@ -369,7 +369,7 @@ class CudaOps:
         plan.arrays[name + "/requests"] = np.asarray(ranges, dtype=np.int32).reshape(-1, 2)
         plan.signature.append(("memory_chunks", tokens))
 
-    MEMORY_MODES = {"gla": 0, "mlstm": 1, "ssd": 2}
+    MEMORY_MODES = {"gla": 0, "mlstm": 1, "ssd": 2, "retention": 3, "wkv": 4}
 
     def matrix_memory_scan(self, ctx, mode, proj, q_off, k_off, v_off, n_head, head_dim, v_dim, gates, constant, state,
                            state_offset=0, qk_group=1, head_consts=None):
@@ -383,20 +383,34 @@ class CudaOps:
         ``"ssd"`` (state-space duality, Mamba-2): ``S <- exp(-exp(A_h) dt) S + dt k v^T``, ``o = S^T q + D_h v`` with
         ``dt = softplus(gates[:, h])``, q and k unscaled and shared by ``qk_group`` neighbouring heads, and
         ``head_consts`` = ``[A_0 .. A_(H-1), D_0 .. D_(H-1)]`` (32-bit).  ``state_offset``: where in a slot the
-        memories begin (a mixer may keep something else in front of them)."""
-        self._want(proj, None, "projection rows", 2)
-        self._want(gates, torch.float32, "gates", 2)
+        memories begin (a mixer may keep something else in front of them).
+
+        ``"retention"``: ``S <- a_h S + (k / sqrt(head_dim)) v^T`` with the fixed decays ``head_consts`` ``[n_head]``, no
+        gates (``None``), q unscaled.  ``"wkv"``: ``o = (S + diag(u) k v^T)^T q`` read before ``S <- diag(w) S + k v^T``,
+        ``w = exp(-exp(gates))`` per key channel, ``head_consts`` the bonus ``u`` ``[n_head * head_dim]``.  ``proj`` may
+        be ``[planes, tokens, columns]`` (q, k, v from projections of their own): an offset is then
+        ``plane * tokens * columns + column``."""
+        planes = proj.dim() == 3
+        self._want(proj, None, "projection rows", 3 if planes else 2)
+        if gates is not None or mode != "retention":
+            self._want(gates, torch.float32, "gates", 2)
         self._want(state, torch.float32, "state slots", 2)
         if mode not in self.MEMORY_MODES:
             raise KernelLibraryError(f"matrix memory: mode {mode!r}")
+        if mode in ("retention", "wkv"):
+            want = n_head if mode == "retention" else n_head * head_dim
+            if head_consts is None or self._want(head_consts, torch.float32, "per-head constants", 1).numel() != want:
+                raise KernelLibraryError(f"matrix memory: the {mode} form wants {want} per-head constants")
         if mode == "ssd" and (head_consts is None or self._want(head_consts, torch.float32, "per-head constants", 1).numel() != 2 * n_head):
             raise KernelLibraryError("matrix memory: the state-space form wants A and D of every head")
         cols_needed = n_head * (v_dim + (1 if mode == "mlstm" else 0)) * head_dim + (n_head if mode == "mlstm" else 0)
         if state_offset < 0 or state_offset + cols_needed > state.shape[1]:
             raise KernelLibraryError("matrix memory: the state slots are too small")
-        n = proj.shape[0]
-        if gates.shape[0] != n:
+        n, ld = proj.shape[-2], proj.shape[-1]
+        if gates is not None and gates.shape[0] != n:
             raise KernelLibraryError("matrix memory: one row of gates per token")
+        gates_ld = gates.shape[1] if gates is not None else 0
+        form = self.MEMORY_MODES[mode] if mode in ("retention", "wkv") else 0
         mlstm = mode == "mlstm"
         out = torch.empty((n, n_head * v_dim), dtype=torch.float32, device=self.device)
         aux = torch.empty((n, n_head, 2), dtype=torch.float32, device=self.device) if mlstm else None
@@ -410,16 +424,16 @@ class CudaOps:
             chunk_state = torch.empty((chunks.shape[0], n_head, cols, head_dim), dtype=torch.float32, device=self.device)
             meta = torch.empty((chunks.shape[0], n_head, 4), dtype=torch.float32, device=self.device) if mlstm else None
             self._run(self.lib.mg_matrix_memory_chunked(
-                _ptr(proj), proj.shape[1], q_off, k_off, v_off, _ptr(gates), gates.shape[1], _ptr(chunks), _ptr(ranges),
+                _ptr(proj), ld, q_off, k_off, v_off, _ptr(gates), gates_ld, _ptr(chunks), _ptr(ranges),
                 _ptr(ctx.req_ctx_before), _ptr(ctx.req_state_slot), state.data_ptr() + 4 * int(state_offset), state.shape[1],
                 _ptr(cum), _ptr(chunk_state), _ptr(meta), _ptr(out), _ptr(aux), chunks.shape[0], tokens, ranges.shape[0], n,
                 n_head, head_dim, v_dim, float(constant), 1 if mlstm else 0, state.shape[0], self._is_bf16(proj),
-                int(qk_group), _ptr(head_consts) if mode == "ssd" else None, self._stream()),
+                int(qk_group), _ptr(head_consts) if mode in ("ssd", "retention", "wkv") else None, form, self._stream()),
                 "matrix memory (chunks)")
             self.launches += 2
             return out, aux
         self._run(self.lib.mg_matrix_memory_scan(
-            _ptr(proj), proj.shape[1], q_off, k_off, v_off, _ptr(gates), gates.shape[1], _ptr(ctx.req_q_start),
+            _ptr(proj), ld, q_off, k_off, v_off, _ptr(gates), gates_ld, _ptr(ctx.req_q_start),
             _ptr(ctx.req_q_len), _ptr(ctx.req_ctx_before), _ptr(ctx.req_state_slot), state.data_ptr() + 4 * int(state_offset),
             state.shape[1], _ptr(out), _ptr(aux), ctx.req_q_start.numel(), n, n_head, head_dim, v_dim, float(constant),
             self.MEMORY_MODES[mode], state.shape[0], self._is_bf16(proj), int(qk_group), _ptr(head_consts), self._stream()),
@@ -433,10 +447,12 @@ class CudaOps:
         ``silu`` or ``sigmoid`` of ``gate`` (a 2-D view of ``n_head * v_dim`` columns), in ``out_dtype``.  Rows whose
         ``positions`` entry is negative (padding) become zeros."""
         self._want(out32, torch.float32, "memory output", 2)
-        self._want(gain, torch.float32, "head gain", 1)
+        if gain is not None:
+            self._want(gain, torch.float32, "head gain", 1)
         n = out32.shape[0]
         if (gate.dtype != out_dtype or gate.dim() != 2 or gate.stride(1) != 1 or gate.shape != (n, n_head * v_dim)
-                or out32.shape[1] != n_head * v_dim or gain.numel() != (n_head * v_dim if per_head_gain else v_dim)):
+                or out32.shape[1] != n_head * v_dim
+                or (gain is not None and gain.numel() != (n_head * v_dim if per_head_gain else v_dim))):
             raise KernelLibraryError("head_norm_gate: shapes do not fit")
         if gate_activation not in ("silu", "sigmoid"):
             raise KernelLibraryError(f"head_norm_gate: gate activation {gate_activation!r}")
@@ -629,10 +645,14 @@ class CudaOps:
               "linear")
         return False
 
-    def linear(self, x, weight, bias, activation, out_dtype):
+    def linear(self, x, weight, bias, activation, out_dtype, out=None):
+        """``act(x W^T + bias)`` in ``out_dtype``; ``out``: a contiguous tensor of that shape and type to write into."""
         if activation not in ("none", "gelu_tanh", "relu_sq"):
             raise KernelLibraryError(f"linear: no epilogue for activation {activation!r}")
-        out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype, device=self.device)
+        if out is None:
+            out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype, device=self.device)
+        elif out.shape != (x.shape[0], weight.shape[0]) or self._want(out, out_dtype, "linear output", 2) is None:
+            raise KernelLibraryError("linear: the output given does not fit")
         self._linear(x, weight, bias, EPILOGUES[activation], out, None)
         return out
 
@@ -1051,12 +1071,17 @@ class CudaOps:
 
     # ---- queries and keys that turn with the position ---------------------------------------------------
     def qk_norm_rotary(self, proj, n_head, n_kv_head, head_dim, v_dim, q_off, k_off, v_off, norm, eps, rot_dims, freq,
-                       cache, slots, positions, q_gain=None, k_gain=None):
+                       cache, slots, positions, q_gain=None, k_gain=None, v_unit_norm=False, v_freq=None):
         """Between a fused projection and the attention: optionally one RMS norm over all query features of a
         token and one over all key features (gains of those whole sizes), then the first ``rot_dims`` features of
         every query and key head turned by ``position * freq[i]`` (``freq``: 32-bit ``[rot_dims / 2]``); queries in
-        place, keys and values to the cache rows ``slots`` (``cache`` None or read-only: nothing is written)."""
+        place, keys and values to the cache rows ``slots`` (``cache`` None or read-only: nothing is written).
+        ``v_unit_norm``: every value head is divided by its root mean square (``eps``, no gain) on its way to the cache;
+        ``v_freq`` (32-bit ``[v_dim / 2]``): all features of every value head then turn by ``position * v_freq[m]``,
+        feature ``m`` paired with ``m + v_dim / 2``."""
         self._want(proj, None, "projection rows", 2)
+        if v_freq is not None and (v_dim % 2 or self._want(v_freq, torch.float32, "value frequencies", 1).numel() != v_dim // 2):
+            raise KernelLibraryError("qk_norm_rotary: one frequency per pair of value features")
         self._want(positions, torch.int32, "positions", 1)
         if rot_dims and self._want(freq, torch.float32, "rotary frequencies", 1).numel() != rot_dims // 2:
             raise KernelLibraryError("qk_norm_rotary: one frequency per pair of turning features")
@@ -1075,7 +1100,136 @@ class CudaOps:
         self._run(self.lib.mg_qk_norm_rotary(
             _ptr(proj), proj.shape[1], proj.shape[0], n_head, n_kv_head, head_dim, v_dim, q_off, k_off, v_off,
             1 if norm else 0, float(eps), _ptr(q_gain), _ptr(k_gain), int(rot_dims), _ptr(freq), _ptr(positions), pages[0],
-            pages[1], pages[2], pages[3], pages[4], self._is_bf16(proj), self._stream()), "qk_norm_rotary")
+            pages[1], pages[2], pages[3], pages[4], self._is_bf16(proj), 1 if v_unit_norm else 0, float(eps), _ptr(v_freq),
+            self._stream()), "qk_norm_rotary")
+
+    def rotate_heads(self, heads, n_head, v_dim, freq, positions, sign=-1.0):
+        """Every head of ``heads`` ``[tokens, n_head * v_dim]`` turned in place by ``sign * position * freq[m]``, feature
+        ``m`` paired with ``m + v_dim / 2`` (``sign`` -1: back into the frame of the token's own position)."""
+        self._want(heads, None, "heads", 2)
+        self._want(positions, torch.int32, "positions", 1)
+        if (heads.shape[1] != n_head * v_dim or v_dim % 2 or positions.numel() != heads.shape[0]
+                or self._want(freq, torch.float32, "frequencies", 1).numel() != v_dim // 2):
+            raise KernelLibraryError("rotate_heads: shapes do not fit")
+        self._run(self.lib.mg_rotate_heads(_ptr(heads), heads.shape[0], n_head, v_dim, _ptr(freq), _ptr(positions),
+                                           float(sign), self._is_bf16(heads), self._stream()), "rotate_heads")
+        return heads
+
+    # ---- recurrences over single features, blends with the token before ------------------------------------
+    def gated_recurrence(self, ctx, pre, z_off, u_off, g_off, width, state, state_offset, out_dtype):
+        """``s <- (1 - sigmoid(z)) s + sigmoid(z) cand(u)`` feature by feature over every request's tokens, from and to
+        the requests' state slots (``width`` numbers from ``state_offset``); ``cand(u) = u + 1/2`` for ``u >= 0`` and
+        ``sigmoid(u)`` below.  ``pre``: 32-bit rows with z, u and an output gate g at the three offsets.  Returns
+        ``s * silu(g)`` ``[tokens, width]`` in ``out_dtype``."""
+        self._want(pre, torch.float32, "pre-activations", 2)
+        self._want(state, torch.float32, "state slots", 2)
+        if state_offset < 0 or state_offset + width > state.shape[1]:
+            raise KernelLibraryError("gated_recurrence: the state slots are too small")
+        n = pre.shape[0]
+        out = torch.empty((n, width), dtype=out_dtype, device=self.device)
+        self._run(self.lib.mg_gated_recurrence(
+            _ptr(pre), pre.shape[1], z_off, u_off, g_off, _ptr(ctx.req_q_start), _ptr(ctx.req_q_len), _ptr(ctx.req_ctx_before),
+            _ptr(ctx.req_state_slot), state.data_ptr() + 4 * int(state_offset), state.shape[1], _ptr(out),
+            ctx.req_q_start.numel(), n, width, state.shape[0], self._is_bf16(out), self._stream()), "gated_recurrence")
+        return out
+
+    def token_shift_mix(self, ctx, x, mu, state):
+        """``out[s] = x_t + (x_(t-1) - x_t) * mu[s]`` for every row of ``mu`` ``[mixes, width]`` (32-bit): ``[mixes, tokens,
+        width]`` in x's type.  The row before a request's first row of the step comes from the head of its state slot
+        (zeros for a sequence's first token); ``conv_state_update`` with two taps leaves the step's last row there."""
+        self._want(x, None, "rows", 2)
+        self._want(mu, torch.float32, "blend weights", 2)
+        self._want(state, torch.float32, "state slots", 2)
+        n, width = x.shape
+        if mu.shape[1] != width or state.shape[1] < width:
+            raise KernelLibraryError("token_shift_mix: shapes do not fit")
+        out = torch.empty((mu.shape[0], n, width), dtype=x.dtype, device=self.device)
+        self._run(self.lib.mg_token_shift_mix(
+            _ptr(x), _ptr(mu), _ptr(ctx.token_request), _ptr(ctx.positions), _ptr(ctx.req_q_start), _ptr(ctx.req_ctx_before),
+            _ptr(ctx.req_state_slot), _ptr(state), state.shape[1], _ptr(out), n, width, mu.shape[0], ctx.req_q_start.numel(),
+            state.shape[0], self._is_bf16(x), self._stream()), "token_shift_mix")
+        return out
+
+    # ---- sums into the residual stream ------------------------------------------------------------------------
+    def zeros32(self, rows, width):
+        """A zeroed 32-bit buffer a sublayer can add its output into."""
+        out = torch.empty((rows, width), dtype=torch.float32, device=self.device)
+        self._run(self.lib.mg_zero_fill(_ptr(out), out.numel() * 4, self._stream()), "zero fill")
+        return out
+
+    def rmsnorm_add(self, residual32, y32, weight, eps, offset=0.0, other32=None, scale=1.0, other_scale=1.0):
+        """``residual32 += rms_norm(scale * y32 [+ other_scale * other32]) * (offset + weight)``, in place, 32-bit."""
+        self._want(residual32, torch.float32, "residual", 2)
+        self._want(y32, torch.float32, "sublayer output", 2)
+        self._want(weight, torch.float32, "norm weight", 1)
+        if other32 is not None:
+            self._want(other32, torch.float32, "second sublayer output", 2)
+        if y32.shape != residual32.shape or weight.numel() != residual32.shape[1] or (other32 is not None and other32.shape != y32.shape):
+            raise KernelLibraryError("rmsnorm_add: shapes do not fit")
+        self._run(self.lib.mg_rmsnorm_add(_ptr(residual32), _ptr(y32), float(scale), _ptr(other32), float(other_scale),
+                                          _ptr(weight), residual32.shape[0], residual32.shape[1], float(eps), float(offset),
+                                          self._stream()), "rmsnorm_add")
+        return residual32
+
+    def add_rows(self, x32, rows32, vector):
+        """``x32 += rows32 + vector`` in place (``rows32`` None: the vector alone; ``vector``: ``[width]`` 32-bit)."""
+        self._want(x32, torch.float32, "stream", 2)
+        self._want(vector, torch.float32, "vector", 1)
+        if rows32 is not None and self._want(rows32, torch.float32, "rows", 2).shape != x32.shape:
+            raise KernelLibraryError("add_rows: shapes do not fit")
+        if vector.numel() != x32.shape[1]:
+            raise KernelLibraryError("add_rows: the vector does not match the width")
+        self._run(self.lib.mg_add_rows(_ptr(x32), _ptr(rows32), _ptr(vector), x32.numel(), x32.shape[1], self._stream()),
+                  "add_rows")
+        return x32
+
+    def scaled_sum_(self, x32, a32, scale_a, b32, scale_b):
+        """``x32 += scale_a * a32 + scale_b * b32`` in place, 32-bit."""
+        for name, t in (("sum", x32), ("first term", a32), ("second term", b32)):
+            self._want(t, torch.float32, name, 2)
+        if a32.shape != x32.shape or b32.shape != x32.shape:
+            raise KernelLibraryError("scaled_sum: shapes do not fit")
+        self._run(self.lib.mg_scaled_sum(_ptr(x32), _ptr(a32), float(scale_a), _ptr(b32), float(scale_b), x32.numel(),
+                                         self._stream()), "scaled_sum")
+        return x32
+
+    def softcap_(self, x32, cap: float):
+        """``x32 <- cap * tanh(x32 / cap)`` in place (32-bit)."""
+        self._want(x32, torch.float32, "softcap input")
+        self._run(self.lib.mg_softcap(_ptr(x32), x32.numel(), float(cap), self._stream()), "softcap")
+        return x32
+
+    def cast(self, x32, out_dtype):
+        """32-bit rows in ``out_dtype`` (the tensor itself if that is 32-bit)."""
+        self._want(x32, torch.float32, "rows")
+        if out_dtype == torch.float32:
+            return x32
+        out = torch.empty(x32.shape, dtype=out_dtype, device=self.device)
+        self._run(self.lib.mg_cast_rows(_ptr(x32), _ptr(out), x32.numel(), 0, self._is_bf16(out), self._stream()), "cast")
+        return out
+
+    def tanh_cast(self, x32, out_dtype):
+        """``tanh(x32)`` in ``out_dtype`` (the tanh itself in 32-bit)."""
+        self._want(x32, torch.float32, "rows")
+        out = torch.empty(x32.shape, dtype=out_dtype, device=self.device)
+        self._run(self.lib.mg_cast_rows(_ptr(x32), _ptr(out), x32.numel(), 1, self._is_bf16(out), self._stream()), "tanh")
+        return out
+
+    def token_gate(self, ctx, gate32, table, offset, out_dtype):
+        """``gelu_tanh(gate32) * table[token, offset : offset + dim]``, ``dim`` the width of ``gate32``, in ``out_dtype``
+        (the table's type).  Tokens that the step before sampled are taken from its ids, as the embedding does."""
+        self._want(gate32, torch.float32, "gate", 2)
+        self._want(table, out_dtype, "token table", 2)
+        n, dim = gate32.shape
+        if offset < 0 or offset + dim > table.shape[1] or ctx.token_ids.numel() != n:
+            raise KernelLibraryError("token_gate: shapes do not fit")
+        source, previous = getattr(ctx, "token_source", None), getattr(ctx, "fed_ids", None)
+        out = torch.empty((n, dim), dtype=out_dtype, device=self.device)
+        self._run(self.lib.mg_token_gate(_ptr(gate32), _ptr(ctx.token_ids), _ptr(ctx.positions), _ptr(source),
+                                         _ptr(previous) if source is not None else None, _ptr(table), table.shape[1], int(offset),
+                                         _ptr(out), n, dim, table.shape[0], previous.numel() if source is not None else 0,
+                                         self._is_bf16(table), self._is_bf16(out), self._stream()), "token_gate")
+        return out
 
     def latent_prepare(self, proj, n_head, q_off, q_dim, rot_dim, low_off, rank, gain, eps, freq, cache, slots, positions):
         """For an attention over cached latents.  Returns ``q`` ``[tokens, n_head * (rank + rot_dim)]`` whose last

@@ -1,5 +1,5 @@
-from . import (attention, block, embedding, gated_attention, latent_attention, layernorm, loop_entry, matrix_memory, mlp, moe,  # noqa: F401  (register)
-               positions, rmsnorm, stream_connection)
+from . import (attention, block, embedding, gated_attention, gated_recurrence, latent_attention, layernorm, loop_entry,  # noqa: F401  (register)
+               matrix_memory, mlp, moe, positions, rmsnorm, stream_connection, token_side)
 from .base import (ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS,
                    POSITION_ENCODINGS, FeedForward, Mixer, Norm, Part, PositionEncoding,
                    register_arrangement, register_embedding, register_feed_forward,

@@ -23,6 +23,8 @@ Interfaces (what a new part must provide):
                     and the number of the pass that begins; it returns a tensor of its own (never ``embedded32``)
 * Connection:       how a sublayer reads from and writes to several residual streams side by side
                     (``read(ctx, streams32) -> (u, zeros)``, ``write(ctx, streams32, y32, then=None)``)
+* SideInput:        ``forward(ctx, residual32)``  something a layer adds to the stream besides its sublayers, read
+                    from the stream itself and from the step's tokens (a per-layer token embedding); in place
 * Block arrangement: a function ``run(ctx, layer, cache, residual32)`` that wires the layer's
                     named parts and returns the tensor that holds the stream (None: in place).
 """
@@ -119,6 +121,11 @@ class Connection(Part):
         raise NotImplementedError
 
 
+class SideInput(Part):
+    def forward(self, ctx, residual32) -> None:
+        raise NotImplementedError
+
+
 class Registry:
     def __init__(self, role: str) -> None:
         self.role = role
@@ -158,6 +165,7 @@ EMBEDDINGS = Registry("embedding")
 HEADS = Registry("output head")
 STREAM_ENTRIES = Registry("stream entry")
 CONNECTIONS = Registry("stream connection")
+SIDE_INPUTS = Registry("side input")
 
 register_norm = NORMS.register
 register_position_encoding = POSITION_ENCODINGS.register
@@ -168,3 +176,4 @@ register_embedding = EMBEDDINGS.register
 register_head = HEADS.register
 register_stream_entry = STREAM_ENTRIES.register
 register_connection = CONNECTIONS.register
+register_side_input = SIDE_INPUTS.register

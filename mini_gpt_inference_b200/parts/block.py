@@ -9,6 +9,10 @@ always write where it reads); an arrangement hands the stream on with ``stream_a
 returns the tensor that holds it at the end (or nothing, if that is the one it was given).
 ``pre_norm``: ``x += mixer(norm1(x)); x += ff(norm2(x))`` (src/minigpt_infer/model.py:112-115).
 ``pre_norm_mixer_only``: ``x += mixer(norm1(x))``, for a layer without a feed-forward.
+``sandwich_norm``: a norm on both sides of each sublayer, ``x += norm1b(mixer(norm1(x)))``, then, if the layer has a
+feed-forward, ``x += norm2b(ff(norm2(x)))``, then, if it has one, the layer's token input (``side_input``), which
+reads the stream and the step's tokens and adds into the stream.  The sublayers add their output into a zeroed
+32-bit buffer; the norm behind them reads it and adds into the stream in one kernel.
 """
 
 from __future__ import annotations
@@ -40,6 +44,10 @@ class Layer:
 
     def parts(self) -> list:
         return list(self._parts.values())
+
+    def get(self, name: str):
+        """The part of that name, or None if the layer has none."""
+        return self._parts.get(name)
 
     def cache_spec(self):
         """What the layer keeps per request: its mixer's wish.  One cache per layer: of several
@@ -80,3 +88,24 @@ def pre_norm_mixer_only(ctx, layer: Layer, cache, residual32):
 
 pre_norm_mixer_only.requires = ("norm1", "mixer")
 register_arrangement("pre_norm_mixer_only")(pre_norm_mixer_only)
+
+
+def sandwich_norm(ctx, layer: Layer, cache, residual32):
+    x = residual32
+    rows, width = x.shape
+    zeros = ctx.ops.zeros32(rows, width)
+    y = stream_after(layer.mixer.forward(ctx, cache, _normed(ctx, layer.norm1, layer.mixer, x), zeros), zeros)
+    layer.norm1b.add_normed(ctx, y, x)
+    ff = layer.get("feed_forward")
+    if ff is not None:
+        zeros = ctx.ops.zeros32(rows, width)
+        y = stream_after(ff.forward(ctx, _normed(ctx, layer.norm2, ff, x), zeros), zeros)
+        layer.norm2b.add_normed(ctx, y, x)
+    side = layer.get("side_input")
+    if side is not None:
+        side.forward(ctx, x)
+    return None
+
+
+sandwich_norm.requires = ("norm1", "mixer", "norm1b")
+register_arrangement("sandwich_norm")(sandwich_norm)

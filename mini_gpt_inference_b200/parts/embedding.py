@@ -30,25 +30,38 @@ class TokenEmbedding(Part):
     takes_token_source = True
 
     def __init__(self, prefix: str, vocab_size: int, width: int, scale: float = 1.0,
-                 tensor_name: str | None = None) -> None:
+                 tensor_name: str | None = None, norm_name: str | None = None, norm_eps: float = 1e-6,
+                 norm_offset: float = 0.0, init: str = "normal") -> None:
         super().__init__(prefix)
         self.vocab_size, self.width, self.scale = vocab_size, width, float(scale)
         self.tensor_name = tensor_name if tensor_name is not None else self.prefix + "weight"
-        self.weight = None
+        # an RMS norm over the embedded rows (32-bit in and out), its gain under ``norm_name``
+        self.norm_name, self.norm_eps, self.norm_offset = norm_name, float(norm_eps), float(norm_offset)
+        self._init = init
+        self.weight = self.norm_weight = None
 
     def tensor_specs(self):
-        return {self.tensor_name: TensorSpec((self.vocab_size, self.width), "matrix")}
+        specs = {self.tensor_name: TensorSpec((self.vocab_size, self.width), "matrix", self._init)}
+        if self.norm_name is not None:
+            specs[self.norm_name] = TensorSpec((self.width,), "vector", "norm_shift" if self.norm_offset == 1.0 else "norm_gain")
+        return specs
 
     def bind(self, tensors) -> None:
         self.weight = tensors.get(self.tensor_name)
+        if self.norm_name is not None:
+            self.norm_weight = tensors.get(self.norm_name)
 
     def forward(self, ctx, position):
         table = position.table() if position is not None else None
         if getattr(ctx, "token_source", None) is not None:
             # some tokens are still on the device where the step before sampled them
-            return ctx.ops.embed(ctx.token_ids, ctx.positions, self.weight, table,
-                                 source=ctx.token_source, previous=ctx.fed_ids, **self._scale_arg())
-        return ctx.ops.embed(ctx.token_ids, ctx.positions, self.weight, table, **self._scale_arg())
+            x = ctx.ops.embed(ctx.token_ids, ctx.positions, self.weight, table,
+                              source=ctx.token_source, previous=ctx.fed_ids, **self._scale_arg())
+        else:
+            x = ctx.ops.embed(ctx.token_ids, ctx.positions, self.weight, table, **self._scale_arg())
+        if self.norm_name is not None:
+            x = ctx.ops.rmsnorm(x, self.norm_weight, self.norm_eps, self.norm_offset, x.dtype)
+        return x
 
     def _scale_arg(self) -> dict:
         return {} if self.scale == 1.0 else {"scale": self.scale}
@@ -128,15 +141,18 @@ class HashedPairEmbedding(Part):
 
 @register_head("linear_head")
 class LinearHead(Part):
-    """``logits = W y`` with a matrix of the head's own (no bias), 32-bit out."""
+    """``logits = W y`` with a matrix of the head's own (no bias), 32-bit out; optionally ``softcap * tanh(logits /
+    softcap)``."""
 
     graph_safe = True
     accepts_deferred_norm = True
 
     def __init__(self, prefix: str, vocab_size: int, width: int, tensor_name: str | None = None,
-                 embedding=None) -> None:
+                 embedding=None, softcap: float | None = None) -> None:
         super().__init__(prefix)
         self.vocab_size, self.width = vocab_size, width
+        # logits <- softcap * tanh(logits / softcap): monotonic, so a greedy choice taken on the way stays right
+        self.softcap = None if not softcap else float(softcap)
         self.tensor_name = tensor_name if tensor_name is not None else self.prefix + "weight"
         self.weight = None
 
@@ -151,5 +167,6 @@ class LinearHead(Part):
         if greedy_out is not None:
             logits, ctx.greedy_taken = ctx.ops.logits(y, self.weight, greedy_out,
                                                       getattr(ctx, "greedy_vocab_limit", None))
-            return logits
-        return ctx.ops.logits(y, self.weight)
+        else:
+            logits = ctx.ops.logits(y, self.weight)
+        return logits if self.softcap is None else ctx.ops.softcap_(logits, self.softcap)

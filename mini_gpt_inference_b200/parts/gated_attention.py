@@ -33,7 +33,11 @@ of every query and key head turn with the token's position, feature ``i`` paired
 angle ``position * rot_base ** (-2 i / rot_dims)``, after the norm; the rest pass unchanged); ``softcap`` (a
 score ``s``, scale included, becomes ``softcap * tanh(s / softcap)``); ``sink`` (a learned number per head, named
 ``sink``, whose exponential is added to the softmax's denominator: it has no key and no value and is neither
-scaled nor capped).
+scaled nor capped); ``value_unit_norm`` (every value head is divided by its root mean square over its features,
+without a gain, and cached so); ``value_rot`` (the value of position ``j``, after that norm, turns by ``j`` over all
+its features, feature ``m`` paired with ``m + v_head_dim / 2``, angle ``j * rot_base ** (-2 m / v_head_dim)``, and is
+cached so; every head's output at position ``i`` is turned back by ``-i`` before the gate and the output projection,
+so that a value enters the sum turned by its distance to the query).
 
 Positions do not enter otherwise unless the model's position encoding rotates q and k.  The four
 matrices are stored apart in the checkpoint (``q``, ``k``, ``v``, ``g``, then ``o`` and the
@@ -67,7 +71,8 @@ class GatedUnitAttention(Mixer):
                  names: dict | None = None, position=None, bias: bool = False, norm_weights: bool = False,
                  values: str = "projected", slope_rate: float | None = None, block_mask: int | None = None,
                  init: str = "normal", norm_scope: str = "head", rot_dims: int = 0, rot_base: float = 10000.0,
-                 softcap: float | None = None, sink: bool = False) -> None:
+                 softcap: float | None = None, sink: bool = False, value_unit_norm: bool = False,
+                 value_rot: bool = False) -> None:
         super().__init__(prefix)
         self.width, self.n_head, self.head_dim = width, n_head, head_dim
         self.n_kv_head = n_head if n_kv_head is None else n_kv_head
@@ -98,7 +103,12 @@ class GatedUnitAttention(Mixer):
             raise ValueError(f"rot_dims {rot_dims}: an even number of at most head_dim ({head_dim}) features")
         self.norm_scope, self.rot_dims, self.rot_base = norm_scope, int(rot_dims), float(rot_base)
         # queries and keys that turn with the position, or are normed across heads, go through another kernel
-        self.turns = self.rot_dims > 0 or norm_scope == "projection"
+        self.value_unit_norm, self.value_rot = bool(value_unit_norm), bool(value_rot)
+        if self.value_rot and self.v_head_dim % 2:
+            raise ValueError(f"value_rot: value heads of {self.v_head_dim} features do not turn in pairs")
+        if self.value_rot and gate:
+            raise ValueError("value_rot: the heads are turned back before any gate; a gated output is not built")
+        self.turns = self.rot_dims > 0 or norm_scope == "projection" or self.value_unit_norm or self.value_rot
         if self.turns and (value_blend is not None or values == "keys" or (unit_norm and not norm_weights
                                                                            and norm_scope == "projection")):
             raise ValueError("rotary positions and the projection-wide norm go with projected, unblended values "
@@ -125,6 +135,7 @@ class GatedUnitAttention(Mixer):
             self.g_off = self.v_off + self.v_width
         self.fused_weight = self.out_weight = self.blend = None
         self.fused_bias = self.out_bias = self.q_gain = self.k_gain = self.slopes = self.sinks = self.freq = None
+        self.v_freq = None
 
     def _name(self, which: str) -> str:
         return self.prefix + self.names[which]
@@ -178,6 +189,9 @@ class GatedUnitAttention(Mixer):
             # f_i = base^(-2 i / n), worked out in 64-bit and handed to the kernel as 32-bit numbers
             freq = [self.rot_base ** (-2.0 * i / self.rot_dims) for i in range(self.rot_dims // 2)]
             self.freq = torch.tensor(freq, dtype=torch.float64).to(dtype=torch.float32, device=self.out_weight.device)
+        if self.value_rot and self.out_weight is not None:
+            freq = [self.rot_base ** (-2.0 * m / self.v_head_dim) for m in range(self.v_head_dim // 2)]
+            self.v_freq = torch.tensor(freq, dtype=torch.float64).to(dtype=torch.float32, device=self.out_weight.device)
         if self.has_norm_weights:
             self.q_gain, self.k_gain = tensors.get(self._name("q") + ".norm"), tensors.get(self._name("k") + ".norm")
         if self.slope_rate is not None and self.out_weight is not None:
@@ -215,6 +229,8 @@ class GatedUnitAttention(Mixer):
         elif self.value_blend == "source":
             ctx.shared[VALUE_SOURCE] = proj[:, self.v_off: self.v_off + self.v_width]
         extra = {"q_gain": self.q_gain, "k_gain": self.k_gain} if self.has_norm_weights else {}
+        if self.value_unit_norm or self.value_rot:
+            extra.update(v_unit_norm=self.value_unit_norm, v_freq=self.v_freq)
         if self.turns:
             ops.qk_norm_rotary(proj, self.n_head, self.n_kv_head, self.head_dim, self.v_head_dim, 0, self.k_off,
                                self.v_off, self.unit_norm, self.eps, self.rot_dims, self.freq, cache,
@@ -235,4 +251,6 @@ class GatedUnitAttention(Mixer):
             extra["sinks"] = self.sinks
         out = ops.paged_attention_general(proj, self.n_head, self.n_kv_head, self.head_dim, self.v_head_dim,
                                           self.scale, cache, ctx, gate=gate, **extra)
+        if self.value_rot:
+            ops.rotate_heads(out, self.n_head, self.v_head_dim, self.v_freq, ctx.positions, -1.0)
         ops.linear_residual(out, self.out_weight, self.out_bias, residual32)

@@ -1,5 +1,5 @@
-"""Mixers whose memory is a matrix per head, carried from token to token: gated linear attention and
-the matrix memory of xLSTM (mLSTM).
+"""Mixers whose memory is a matrix per head, carried from token to token: gated linear attention, the matrix
+memory of xLSTM (mLSTM), retention, RWKV-style time mixing (``wkv``) and the state-space form of Mamba-2.
 
 Both project ``q`` and ``k`` (``n_head x head_dim``, ``q`` times ``head_dim ** -0.5``), ``v`` and an
 output gate ``g`` (``n_head x v_head_dim``), keep per head a state ``S`` of ``head_dim x v_head_dim``
@@ -60,7 +60,7 @@ class _MatrixMemoryMixer(Mixer):
             return False
         self.fused_weight = torch.cat(rows, dim=0).contiguous()
         self.out_weight = tensors.get(p + "o")
-        self.norm_gain = tensors.get(p + "norm")
+        self.norm_gain = tensors.get(p + "norm")      # (None for a mixer whose heads have no gain)
         return True
 
     def plan_step(self, batch, plan, ops) -> None:
@@ -160,6 +160,126 @@ class MLSTM(_MatrixMemoryMixer):
         out, aux = ops.matrix_memory_scan(ctx, "mlstm", proj, 0, self.k_off, self.v_off, self.n_head, self.head_dim,
                                           self.v_head_dim, gates, self.gate_cap, cache.state)
         self._finish(ctx, proj, out, aux, residual32, True, "sigmoid")
+
+
+@register_mixer("retention")
+class Retention(_MatrixMemoryMixer):
+    """Linear attention with one fixed decay per head and no softmax or denominator: ``S_t = a_h S_(t-1) +
+    (k_t / sqrt(head_dim)) v_t^T``, ``o_t = S_t^T q_t`` (``q`` unscaled), ``decay`` the list of the heads' ``a_h``.
+    Every head's ``o`` is divided by its root mean square (no gain), the heads are multiplied by ``silu(g)`` and
+    projected.  The decays are 32-bit numbers worked out from the list once."""
+
+    mode = "retention"
+
+    def __init__(self, prefix: str, width: int, n_head: int, head_dim: int, v_head_dim: int, decay, eps: float,
+                 position=None) -> None:
+        super().__init__(prefix, width, n_head, head_dim, v_head_dim, eps)
+        self.decay = [float(a) for a in decay]
+        if len(self.decay) != n_head or not all(0.0 <= a <= 1.0 for a in self.decay):
+            raise ValueError(f"decay: {n_head} numbers in 0..1, one per head (got {list(decay)!r})")
+        self.decays = None
+
+    def tensor_specs(self):
+        return self._main_specs()
+
+    def bind(self, tensors) -> None:
+        if self._bind_main(tensors):
+            self.decays = torch.tensor(self.decay, dtype=torch.float64).to(dtype=torch.float32,
+                                                                            device=self.out_weight.device)
+
+    def cache_spec(self):
+        return FixedStateSpec((self.n_head * self.v_head_dim * self.head_dim,), "float32")
+
+    def forward(self, ctx, cache, y, residual32) -> None:
+        ops = ctx.ops
+        proj = ops.linear(y, self.fused_weight, None, "none", ctx.act_dtype)
+        out, aux = ops.matrix_memory_scan(ctx, "retention", proj, 0, self.k_off, self.v_off, self.n_head, self.head_dim,
+                                          self.v_head_dim, None, 0.0, cache.state, head_consts=self.decays)
+        self._finish(ctx, proj, out, aux, residual32, False, "silu")
+
+
+@register_mixer("wkv")
+class WKV(Mixer):
+    """RWKV-6 style time mixing.  With ``h'`` the input of the token before (zeros for a sequence's first token), each
+    of r, k, v, g, w reads its own blend ``h + (h' - h) * mu_s`` (``mu.r`` ... ``mu.w``, ``[width]`` each).  ``r``, ``k``,
+    ``v`` are ``n_head x head_dim`` projections of their blends (tensors ``r``, ``k``, ``v``), the gate is
+    ``silu(W_g blend_g)``, the decay per head and key channel ``w = exp(-exp(W_w2 tanh(W_w1 blend_w) + w0))`` (``w1``,
+    ``w2``: two thin matrices whose inner size the checkpoint gives).  Per head ``o_t = (S_(t-1) + diag(u) k_t
+    v_t^T)^T r_t`` with the bonus ``u`` ``[n_head, head_dim]`` for the current token only, then ``S_t = diag(w_t)
+    S_(t-1) + k_t v_t^T``.  Every head's ``o`` is divided by its root mean square, the concatenated heads times
+    ``norm``, times the gate, are projected by ``o``.
+
+    A request's state slot holds the last input ``h`` (32-bit), then the memories.  The decays' pre-activations come
+    from a projection that writes 32-bit; their exponentials, the memories and the norm are 32-bit whatever the
+    compute dtype.
+    """
+
+    graph_safe = True      # launches kernels only; the state slot and the token counts are read on the device
+    accepts_deferred_norm = True
+    mode = "wkv"
+    DEFAULT_DECAY_RANK = 16      # what random-weights mode gives the two decay matrices (a checkpoint's shapes win)
+    MIXES = ("r", "k", "v", "g", "w")
+
+    def __init__(self, prefix: str, width: int, n_head: int, head_dim: int, eps: float, position=None) -> None:
+        super().__init__(prefix)
+        self.width, self.n_head, self.head_dim, self.eps = width, n_head, head_dim, float(eps)
+        self.inner = n_head * head_dim
+        self.mu = self.weights = self.decay_in = self.decay_out = self.decay_bias = None
+        self.bonus = self.norm_gain = self.out_weight = None
+
+    def tensor_specs(self):
+        p, c, n, r = self.prefix, self.width, self.inner, self.DEFAULT_DECAY_RANK
+        specs = {p + "mu." + s: TensorSpec((c,), "vector", "unit_interval") for s in self.MIXES}
+        for s in ("r", "k", "v", "g"):
+            specs[p + s] = TensorSpec((n, c), "matrix", "fan_in")
+        specs[p + "w1"] = TensorSpec((-1, c), "matrix", "fan_in", fill=(r, c))
+        specs[p + "w2"] = TensorSpec((n, -1), "matrix", "fan_in", fill=(n, r))
+        specs[p + "w0"] = TensorSpec((n,), "vector", "unit_normal")
+        specs[p + "u"] = TensorSpec((self.n_head, self.head_dim), "vector", "unit_normal")
+        specs[p + "norm"] = TensorSpec((n,), "vector", "norm_gain")
+        specs[p + "o"] = TensorSpec((c, n), "matrix", "fan_in_residual")
+        return specs
+
+    def bind(self, tensors) -> None:
+        p = self.prefix
+        if tensors.get(p + "o") is None:
+            return
+        self.mu = torch.stack([tensors[p + "mu." + s] for s in self.MIXES]).contiguous()
+        self.weights = [tensors[p + s] for s in ("r", "k", "v", "g")]
+        self.decay_in, self.decay_out, self.decay_bias = tensors[p + "w1"], tensors[p + "w2"], tensors[p + "w0"]
+        if self.decay_in.shape[0] != self.decay_out.shape[1]:
+            raise ValueError(f"{p}w1 {tuple(self.decay_in.shape)} and {p}w2 {tuple(self.decay_out.shape)} "
+                             "do not share their inner size")
+        self.bonus = tensors[p + "u"].reshape(-1).contiguous()
+        self.norm_gain, self.out_weight = tensors[p + "norm"], tensors[p + "o"]
+
+    def cache_spec(self):
+        return FixedStateSpec((self.width + self.n_head * self.head_dim * self.head_dim,), "float32")
+
+    def plan_step(self, batch, plan, ops) -> None:
+        planner = getattr(ops, "plan_memory_chunks", None)
+        if planner is not None:
+            planner(batch, plan, self.head_dim, self.head_dim, False)
+
+    def forward(self, ctx, cache, y, residual32) -> None:
+        ops = ctx.ops
+        if hasattr(y, "materialize"):
+            y = y.materialize()
+        n = y.shape[0]
+        blends = ops.token_shift_mix(ctx, y, self.mu, cache.state)                  # [5, tokens, width]
+        ops.conv_state_update(ctx, y, 0, self.width, 2, cache.state)                # the step's last input
+        proj = torch.empty((4, n, self.inner), dtype=ctx.act_dtype, device=y.device)  # planes r, k, v, g
+        for i, weight in enumerate(self.weights):
+            ops.linear(blends[i], weight, None, "none", ctx.act_dtype, out=proj[i])
+        thin = ops.linear(blends[4], self.decay_in, None, "none", torch.float32)
+        thin = ops.tanh_cast(thin, ctx.act_dtype)
+        z = ops.linear(thin, self.decay_out, self.decay_bias, "none", torch.float32)
+        plane = n * self.inner
+        out, _ = ops.matrix_memory_scan(ctx, "wkv", proj, 0, plane, 2 * plane, self.n_head, self.head_dim, self.head_dim,
+                                        z, 0.0, cache.state, state_offset=self.width, head_consts=self.bonus)
+        heads = ops.head_norm_gate(out, None, proj[3], self.norm_gain, self.n_head, self.head_dim, self.eps, True, "silu",
+                                   ctx.act_dtype, positions=ctx.positions)
+        ops.linear_residual(heads, self.out_weight, None, residual32)
 
 
 @register_mixer("state_space_duality")

@@ -11,7 +11,7 @@ from __future__ import annotations
 from typing import Any, Mapping
 
 from .base import (ARRANGEMENTS, CONNECTIONS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS,
-                   POSITION_ENCODINGS, STREAM_ENTRIES)
+                   POSITION_ENCODINGS, SIDE_INPUTS, STREAM_ENTRIES)
 from .block import Layer, stream_after
 from .spec import ModelSpec, TensorSpec
 
@@ -30,7 +30,8 @@ class DecoderModel:
                 if role == "mixer":
                     parts[name] = MIXERS.build(part_spec, p, position=self.position)
                 else:
-                    registry = {"norm": NORMS, "feed_forward": FEED_FORWARDS, "connection": CONNECTIONS}[role]
+                    registry = {"norm": NORMS, "feed_forward": FEED_FORWARDS, "connection": CONNECTIONS,
+                                "side_input": SIDE_INPUTS}[role]
                     parts[name] = registry.build(part_spec, p)
             self.layers.append(Layer(parts, roles, ARRANGEMENTS.get(layer_spec.arrangement), p))
         self.entries = [STREAM_ENTRIES.build(entry, "") for entry in spec.entries]

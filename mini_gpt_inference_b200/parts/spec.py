@@ -12,7 +12,7 @@ from dataclasses import dataclass, field
 from typing import Any, Mapping
 
 
-ROLES = ("norm", "mixer", "feed_forward", "connection")
+ROLES = ("norm", "mixer", "feed_forward", "connection", "side_input")
 
 
 @dataclass(frozen=True)
@@ -20,7 +20,7 @@ class PartSpec:
     kind: str                               # key in the part registry of its role
     params: Mapping[str, Any] = field(default_factory=dict)
     name: str = ""                          # weight-name prefix inside its parent ("ln1", "attn")
-    role: str = ""                          # inside a layer: "norm" | "mixer" | "feed_forward" | "connection"; if empty,
+    role: str = ""                          # inside a layer: "norm" | "mixer" | "feed_forward" | "connection" | "side_input"; if empty,
                                             # taken from the part's name in the layer (see LayerSpec)
 
 

@@ -28,7 +28,10 @@ class TorchOps:
             y = y + shift
         return y.to(out_dtype)
 
-    def linear(self, x, weight, bias, activation, out_dtype):
+    def linear(self, x, weight, bias, activation, out_dtype, out=None):
+        if out is not None:
+            out.copy_(self.linear(x, weight, bias, activation, out_dtype))
+            return out
         y = x.float() @ weight.float().T
         if bias is not None:
             y = y + bias
@@ -225,6 +228,9 @@ class TorchOps:
 
     def matrix_memory_scan(self, ctx, mode, proj, q_off, k_off, v_off, n_head, head_dim, v_dim, gates, constant, state,
                            state_offset=0, qk_group=1, head_consts=None):
+        if mode in ("retention", "wkv"):
+            return self._fixed_or_bonus_scan(ctx, mode, proj, q_off, k_off, v_off, n_head, head_dim, v_dim, gates, state,
+                                             state_offset, head_consts), None
         n = proj.shape[0]
         if mode == "ssd":
             return self._state_space_scan(ctx, proj, q_off, k_off, v_off, n_head, head_dim, v_dim, gates, state,
@@ -269,6 +275,44 @@ class TorchOps:
                 flat[n_head * cols * head_dim:] = m
         return out.reshape(n, n_head * v_dim), aux
 
+    def _fixed_or_bonus_scan(self, ctx, mode, proj, q_off, k_off, v_off, n_head, head_dim, v_dim, gates, state, state_offset,
+                             head_consts):
+        """Retention (a fixed decay per head, keys scaled) and the wkv form (the read before the update, with a bonus
+        on the token itself); ``proj`` may be planes ``[planes, tokens, columns]`` with offsets that name a plane."""
+        n, ld = proj.shape[-2], proj.shape[-1]
+        flat_rows = proj.reshape(-1, ld)
+
+        def take(off, size):
+            plane, col = divmod(int(off), n * ld) if proj.dim() == 3 else (0, int(off))
+            return flat_rows[plane * n: (plane + 1) * n, col: col + size].float()
+        q = take(q_off, n_head * head_dim).reshape(n, n_head, head_dim)
+        k = take(k_off, n_head * head_dim).reshape(n, n_head, head_dim)
+        v = take(v_off, n_head * v_dim).reshape(n, n_head, v_dim)
+        if mode == "retention":
+            k = k * head_dim ** -0.5
+        out = torch.zeros(n, n_head, v_dim)
+        size = n_head * v_dim * head_dim
+        for r in range(ctx.num_requests):
+            start, count = int(ctx.req_q_start[r]), int(ctx.req_q_len[r])
+            if count == 0:
+                continue
+            flat = state[int(ctx.req_state_slot[r])]
+            S = flat[state_offset: state_offset + size].view(n_head, v_dim, head_dim).clone()
+            if int(ctx.req_ctx_before[r]) == 0:
+                S.zero_()
+            for i in range(start, start + count):
+                kv = v[i][:, :, None] * k[i][:, None, :]
+                if mode == "retention":
+                    S = head_consts.float()[:, None, None] * S + kv
+                    out[i] = torch.einsum("hvd,hd->hv", S, q[i])
+                else:
+                    bonus = head_consts.float().view(n_head, 1, head_dim)
+                    out[i] = torch.einsum("hvd,hd->hv", S + bonus * kv, q[i])
+                    decay = torch.exp(-torch.exp(gates[i].float())).view(n_head, 1, head_dim)
+                    S = decay * S + kv
+            flat[state_offset: state_offset + size] = S.reshape(-1)
+        return out.reshape(n, n_head * v_dim)
+
     def _state_space_scan(self, ctx, proj, q_off, k_off, v_off, n_head, n_state, v_dim, steps, state, state_offset,
                           qk_group, head_consts):
         n, groups = proj.shape[0], n_head // qk_group
@@ -300,8 +344,9 @@ class TorchOps:
         if aux is not None:
             o = o / (torch.maximum(aux[:, :, 0].abs(), torch.exp(-aux[:, :, 1])) + 1e-6)[:, :, None]
         o = o / torch.sqrt((o * o).mean(-1, keepdim=True) + eps)
-        o = o * (gain.view(n_head, v_dim) if per_head_gain else gain)
-        g = gate.float().view(n, n_head, v_dim)
+        if gain is not None:
+            o = o * (gain.view(n_head, v_dim) if per_head_gain else gain)
+        g = gate.float().reshape(n, n_head, v_dim)
         g = g * torch.sigmoid(g) if gate_activation == "silu" else torch.sigmoid(g)
         return (o * g).reshape(n, n_head * v_dim).to(out_dtype)
 
@@ -349,7 +394,7 @@ class TorchOps:
         return torch.cat([u * cos - v * sin, v * cos + u * sin, x[..., rot_dims:]], dim=-1)
 
     def qk_norm_rotary(self, proj, n_head, n_kv_head, head_dim, v_dim, q_off, k_off, v_off, norm, eps, rot_dims, freq,
-                       cache, slots, positions, q_gain=None, k_gain=None):
+                       cache, slots, positions, q_gain=None, k_gain=None, v_unit_norm=False, v_freq=None):
         n = proj.shape[0]
         live = positions >= 0
 
@@ -360,6 +405,10 @@ class TorchOps:
         k = whole(proj[:, k_off: k_off + n_kv_head * head_dim].float(), k_gain).reshape(n, n_kv_head, head_dim)
         q, k = self._turn(q, positions, rot_dims, freq), self._turn(k, positions, rot_dims, freq)
         v = proj[:, v_off: v_off + n_kv_head * v_dim].float().reshape(n, n_kv_head, v_dim)
+        if v_unit_norm:
+            v = v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps)
+        if v_freq is not None:
+            v = self._turn(v, positions, v_dim, v_freq)
         proj[live, q_off: q_off + n_head * head_dim] = q[live].reshape(int(live.sum()), -1).to(proj.dtype)
         if cache is not None and cache.writes:
             keep = live & (slots >= 0)
@@ -437,3 +486,77 @@ class TorchOps:
         y = (out32 * g * torch.sigmoid(g)).view(n, parts, width // parts)
         y = y / torch.sqrt((y * y).mean(-1, keepdim=True) + eps)
         return (y.reshape(n, width) * gain).to(out_dtype)
+
+    def rotate_heads(self, heads, n_head, v_dim, freq, positions, sign=-1.0):
+        n = heads.shape[0]
+        turned = self._turn(heads.float().reshape(n, n_head, v_dim), positions, v_dim, sign * freq.float())
+        live = positions >= 0
+        heads[live] = turned.reshape(n, -1)[live].to(heads.dtype)
+        return heads
+
+    def gated_recurrence(self, ctx, pre, z_off, u_off, g_off, width, state, state_offset, out_dtype):
+        n = pre.shape[0]
+        z = torch.sigmoid(pre[:, z_off: z_off + width])
+        u = pre[:, u_off: u_off + width]
+        cand = torch.where(u >= 0, u + 0.5, torch.sigmoid(u))
+        g = pre[:, g_off: g_off + width]
+        out = torch.zeros(n, width)
+        for r in range(ctx.num_requests):
+            start, count = int(ctx.req_q_start[r]), int(ctx.req_q_len[r])
+            if count == 0:
+                continue
+            slot = int(ctx.req_state_slot[r])
+            s = state[slot, state_offset: state_offset + width].clone()
+            if int(ctx.req_ctx_before[r]) == 0:
+                s.zero_()
+            for i in range(start, start + count):
+                s = (1 - z[i]) * s + z[i] * cand[i]
+                out[i] = s * g[i] * torch.sigmoid(g[i])
+            state[slot, state_offset: state_offset + width] = s
+        return out.to(out_dtype)
+
+    def token_shift_mix(self, ctx, x, mu, state):
+        n, width = x.shape
+        before = torch.zeros(n, width)
+        for r in range(ctx.num_requests):
+            start, count = int(ctx.req_q_start[r]), int(ctx.req_q_len[r])
+            if count == 0:
+                continue
+            if int(ctx.req_ctx_before[r]) > 0:
+                before[start] = state[int(ctx.req_state_slot[r]), :width]
+            before[start + 1: start + count] = x[start: start + count - 1].float()
+        cur = x.float()
+        return (cur[None] + (before - cur)[None] * mu.float()[:, None, :]).to(x.dtype)
+
+    def zeros32(self, rows, width):
+        return torch.zeros(rows, width)
+
+    def rmsnorm_add(self, residual32, y32, weight, eps, offset=0.0, other32=None, scale=1.0, other_scale=1.0):
+        y = scale * y32 if other32 is None else scale * y32 + other_scale * other32
+        residual32 += y / torch.sqrt((y * y).mean(-1, keepdim=True) + eps) * (offset + weight)
+        return residual32
+
+    def add_rows(self, x32, rows32, vector):
+        x32 += vector if rows32 is None else rows32 + vector
+        return x32
+
+    def scaled_sum_(self, x32, a32, scale_a, b32, scale_b):
+        x32 += scale_a * a32 + scale_b * b32
+        return x32
+
+    def softcap_(self, x32, cap):
+        x32.copy_(cap * torch.tanh(x32 / cap))
+        return x32
+
+    def cast(self, x32, out_dtype):
+        return x32.to(out_dtype)
+
+    def tanh_cast(self, x32, out_dtype):
+        return torch.tanh(x32).to(out_dtype)
+
+    def token_gate(self, ctx, gate32, table, offset, out_dtype):
+        dim = gate32.shape[1]
+        e = table.float()[ctx.token_ids.long().clamp(min=0), offset: offset + dim]
+        z = gate32
+        act = 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)))
+        return (act * e).to(out_dtype)
