@@ -15,6 +15,9 @@ pinned buffer and cross to the device in one copy.
 
 from __future__ import annotations
 
+import contextlib
+import gc
+
 from array import array
 from dataclasses import dataclass, field
 from typing import Sequence
@@ -27,6 +30,20 @@ from ..cache.storage import CacheStorage
 from ..parts.base import Part
 from ..parts.context import HostBatch, StepContext, StepPlan
 from ..parts.model import DecoderModel
+
+
+
+@contextlib.contextmanager
+def _no_collection():
+    """No garbage collection while a graph is captured: an object freed then (an old graph, a tensor of a runner that
+    is gone) would call into the driver, which is not allowed while a stream captures, and the capture would be lost."""
+    was = gc.isenabled()
+    gc.disable()
+    try:
+        yield
+    finally:
+        if was:
+            gc.enable()
 
 
 class StepError(ValueError):
@@ -403,7 +420,7 @@ class ModelRunner:
         if dependent is not None:
             dependent(True)
         try:
-            with torch.cuda.graph(graph, pool=self._graph_pool):
+            with _no_collection(), torch.cuda.graph(graph, pool=self._graph_pool):
                 if not fused_fetch:
                     self.ops.gather_tokens(ctx.token_ids, sources, self.sampled_ids)
                 # this step's greedy choice is left where the next step looks for it: by the head
@@ -593,7 +610,7 @@ class ModelRunner:
         if dependent is not None:
             dependent(True)
         try:
-            with torch.cuda.graph(graph, pool=self._graph_pool):
+            with _no_collection(), torch.cuda.graph(graph, pool=self._graph_pool):
                 state.logits = self._forward(ctx)
         finally:
             if dependent is not None:

@@ -29,7 +29,24 @@ def _moe(experts, top, ff):
     return {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
 
 
-def config(which: str) -> dict:
+def all_experts(raw: dict) -> dict:
+    """The same configuration with every router choosing all its experts (the weights stay a softmax).  A choice
+    among experts is discrete: where two router logits are close, the rounding of bfloat16 activations can turn it,
+    and the two sides then compute different functions.  Whole models are therefore compared with real choices in
+    32-bit and with all experts in bfloat16; the router alone is compared in both formats."""
+    for layer in raw["layers"]:
+        if layer.get("mlp") is not None:
+            layer["mlp"]["router"]["top"] = layer["mlp"]["router"]["experts"]
+    return raw
+
+
+def config(which: str, every_expert: bool = False) -> dict:
+    if every_expert:
+        return all_experts(config(which))
+    return _config(which)
+
+
+def _config(which: str) -> dict:
     """A: every mixer, a loop of two passes over the first three of four layers, a token input per layer, grouped key
     heads, part of a head rotated, a layer without a feed-forward.  B: the loop in the middle (a layer before it and
     one after it), three passes, as many key heads as query heads, whole heads rotated, one chosen expert, value heads
@@ -122,10 +139,15 @@ PAGE_TOKENS = {"A": 8, "B": 16, "C": 4, "D": 16, "E": 8}
 DECAY_RANK = 6          # inner size of the two thin decay matrices of the tests' wkv layers
 
 
-def random_weights(raw: dict, seed: int, dtype=torch.float32, sharp: float = 1.0, as_bfloat16: bool = False) -> dict:
+def random_weights(raw: dict, seed: int, dtype=torch.float32, sharp: float = 1.0, as_bfloat16: bool = False,
+                   steady: bool = False) -> dict:
     """Weights with unit-variance activations: matrices ``N(0, 1 / inputs)``, norm weights ``1 + N(0, 0.3)``, biases
     ``N(0, 0.3)``, embeddings ``N(0, 1)``, blend weights in 0..1.  ``sharp`` scales the attention's query projection
-    (a softmax that leans on few keys).  ``as_bfloat16``: every number is one that bfloat16 holds."""
+    (a softmax that leans on few keys).  ``as_bfloat16``: every number is one that bfloat16 holds.  ``steady``: the
+    matrix memories' query matrices lean towards their key matrices and the wkv bonus is positive, so that a token's
+    read-out of its own key is well away from zero.  (Every head's read-out is divided by its root mean square:
+    where it is one term, as for a sequence's first tokens, and that term nearly cancels, the norm magnifies the
+    rounding of bfloat16 queries and keys without bound.  Runs in bfloat16 use steady weights; 32-bit runs do not.)"""
     gen = torch.Generator().manual_seed(seed)
     c = raw["width"]
 
@@ -150,6 +172,8 @@ def random_weights(raw: dict, seed: int, dtype=torch.float32, sharp: float = 1.0
             h, d, dv = m["heads"], m["dim"], m["vdim"]
             w[x + "q"], w[x + "k"], w[x + "v"], w[x + "g"] = mat(h * d, c), mat(h * d, c), mat(h * dv, c), mat(h * dv, c)
             w[x + "o"] = mat(c, h * dv)
+            if steady:
+                w[x + "q"] = w[x + "k"] + 0.5 * w[x + "q"]
         elif layer["type"] == "wkv":
             h, d = m["heads"], m["dim"]
             for s in "rkvgw":
@@ -158,6 +182,8 @@ def random_weights(raw: dict, seed: int, dtype=torch.float32, sharp: float = 1.0
                 w[x + s] = mat(h * d, c)
             w[x + "w1"], w[x + "w2"], w[x + "w0"] = mat(DECAY_RANK, c), mat(h * d, DECAY_RANK, 2.0), vec(h * d, 1.0) - 1.0
             w[x + "u"], w[x + "norm"], w[x + "o"] = vec(h * d, 0.5).view(h, d), 1.0 + vec(h * d), mat(c, h * d)
+            if steady:
+                w[x + "r"], w[x + "mu.r"], w[x + "u"] = w[x + "k"] + 0.5 * w[x + "r"], w[x + "mu.k"].clone(), w[x + "u"].abs() + 0.5
         else:
             a, n = m["left"], m["right"]["width"]
             w[x + "left.q"] = mat(a["heads"] * a["dim"], c, sharp)
@@ -191,6 +217,17 @@ def plain_logits(raw: dict, tensors: dict, tokens, rows=None, dtype=torch.float6
     return out if rows is None else out[list(rows)]
 
 
+def rounding_spread(raw: dict, tensors: dict, tokens, rows=None) -> torch.Tensor:
+    """Per row: how far the logits move (over the row's spread) when the activations between matrix products are
+    rounded to bfloat16 in the plain implementation and nothing else changes.  The design divides sublayer outputs and heads by their root mean square,
+    so a row where a sum nearly cancels magnifies rounding many times over; a bfloat16 run is held to its tolerance
+    plus three times this."""
+    exact = plain_lunelorn.forward(raw, tensors, tokens)
+    moved = plain_lunelorn.forward(raw, tensors, tokens, round_inputs=torch.bfloat16)
+    err = relative_error(moved, exact)
+    return err if rows is None else err[list(rows)]
+
+
 def plain_greedy(raw: dict, tensors: dict, prompt, new_tokens: int) -> list[int]:
     return plain_lunelorn.greedy(raw, tensors, prompt, new_tokens)
 
@@ -201,14 +238,16 @@ def relative_error(got: torch.Tensor, want: torch.Tensor) -> torch.Tensor:
     return (got.double().cpu() - want).abs().amax(-1) / want.std(-1)
 
 
-def assert_rows_close(got, want, tol, what: str, places=None, outliers: float = 0.0) -> None:
+def assert_rows_close(got, want, tol, what: str, places=None, outliers: float = 0.0, slack=None) -> None:
     """``outliers``: the share of rows (at least one, if not zero) that may miss ``tol``, though not five times
-    ``tol`` (bfloat16 runs: a unit norm after a read-out that nearly cancels magnifies one token's rounding)."""
+    ``tol`` (bfloat16 runs: a unit norm after a read-out that nearly cancels magnifies one token's rounding).
+    ``slack``: per row, what rounding alone does (``rounding_spread``); three times it is added to ``tol``."""
     err = relative_error(got, want)
-    bad = (~(err <= tol)).nonzero()
+    limit = tol if slack is None else tol + 3.0 * slack
+    bad = (~(err <= limit)).nonzero()
     if outliers and 0 < bad.numel() <= max(1, int(outliers * err.numel())):
-        bad = (~(err <= 5 * tol)).nonzero()
+        bad = (~(err <= 5 * limit)).nonzero()
     if bad.numel():
         i = int(bad[0])
         raise AssertionError(f"{what}: first wrong logits at {places[i] if places is not None else i}: "
-                             f"error {float(err[i]):.3e} of the row's spread > {tol:.1e}")
+                             f"error {float(err[i]):.3e} of the row's spread > {float(limit[i]) if slack is not None else tol:.1e}")

@@ -31,6 +31,13 @@ import torch
 
 
 # ---- pieces --------------------------------------------------------------------------------------
+ROUND = None      # a dtype through which activations between two products are rounded (see ``forward``), or None
+
+
+def _r(x):
+    return x if ROUND is None else x.to(ROUND).to(x.dtype)
+
+
 def rms_norm(x, w, eps):
     y = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
     return y if w is None else y * w
@@ -62,9 +69,9 @@ def retention_mixer(h, w, p, m, eps):
     T = h.shape[0]
     H, d = m["heads"], m["dim"]
     dv = m.get("vdim", d)
-    q = (h @ w[p + "q"].T).view(T, H, d)
-    k = (h @ w[p + "k"].T).view(T, H, d) * d ** -0.5
-    v = (h @ w[p + "v"].T).view(T, H, dv)
+    q = _r(h @ w[p + "q"].T).view(T, H, d)
+    k = _r(h @ w[p + "k"].T).view(T, H, d) * d ** -0.5
+    v = _r(h @ w[p + "v"].T).view(T, H, dv)
     decay = torch.tensor(m["decay"], dtype=h.dtype)
     S = torch.zeros(H, d, dv, dtype=h.dtype)
     out = []
@@ -72,7 +79,7 @@ def retention_mixer(h, w, p, m, eps):
         S = decay[:, None, None] * S + k[t][:, :, None] * v[t][:, None, :]
         out.append(torch.einsum("hde,hd->he", S, q[t]))
     o = rms_norm(torch.stack(out), None, eps).reshape(T, H * dv)
-    return (o * silu(h @ w[p + "g"].T)) @ w[p + "o"].T
+    return _r(o * silu(_r(h @ w[p + "g"].T))) @ w[p + "o"].T
 
 
 def rotated_value_attention(h, w, p, m, eps):
@@ -80,16 +87,16 @@ def rotated_value_attention(h, w, p, m, eps):
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     rot = m.get("rot") or {"dims": 0, "base": 1.0}
     pos = torch.arange(T)
-    q = rotate((h @ w[p + "q"].T).view(T, H, d), pos, rot["dims"], rot["base"])
-    k = rotate((h @ w[p + "k"].T).view(T, G, d), pos, rot["dims"], rot["base"])
-    v = rms_norm((h @ w[p + "v"].T).view(T, G, dv), None, eps)
-    v = rotate(v, pos, dv, rot["base"])
+    q = _r(rotate(_r(h @ w[p + "q"].T).view(T, H, d), pos, rot["dims"], rot["base"]))
+    k = _r(rotate(_r(h @ w[p + "k"].T).view(T, G, d), pos, rot["dims"], rot["base"]))
+    v = rms_norm(_r(h @ w[p + "v"].T).view(T, G, dv), None, eps)
+    v = _r(rotate(v, pos, dv, rot["base"]))
     rep = H // G
     k, v = k.repeat_interleave(rep, dim=1), v.repeat_interleave(rep, dim=1)
     s = torch.einsum("ihd,jhd->hij", q, k) * m["scale"]
     s = s.masked_fill(pos[None, :, None] < pos[None, None, :], float("-inf"))
     o = torch.einsum("hij,jhe->ihe", torch.softmax(s, dim=-1), v)
-    o = rotate(o, pos, dv, rot["base"], sign=-1.0)
+    o = _r(rotate(_r(o), pos, dv, rot["base"], sign=-1.0))
     return o.reshape(T, H * dv) @ w[p + "o"].T
 
 
@@ -103,7 +110,7 @@ def gated_recurrence(h, w, p, m):
     for t in range(T):
         s = (1 - z[t]) * s + z[t] * cand[t]
         out.append(s)
-    return (torch.stack(out) * silu(h @ w[p + "g"].T)) @ w[p + "o"].T
+    return _r(torch.stack(out) * silu(h @ w[p + "g"].T)) @ w[p + "o"].T
 
 
 def parallel_mixer(h, w, p, m, eps):
@@ -118,12 +125,12 @@ def wkv_mixer(h, w, p, m, eps):
     before = torch.cat([torch.zeros_like(h[:1]), h[:-1]], dim=0)
 
     def blend(name):
-        return h + (before - h) * w[p + "mu." + name]
-    r = (blend("r") @ w[p + "r"].T).view(T, H, d)
-    k = (blend("k") @ w[p + "k"].T).view(T, H, d)
-    v = (blend("v") @ w[p + "v"].T).view(T, H, d)
-    gate = silu(blend("g") @ w[p + "g"].T)
-    decay = torch.exp(-torch.exp(torch.tanh(blend("w") @ w[p + "w1"].T) @ w[p + "w2"].T + w[p + "w0"])).view(T, H, d)
+        return _r(h + (before - h) * w[p + "mu." + name])
+    r = _r(blend("r") @ w[p + "r"].T).view(T, H, d)
+    k = _r(blend("k") @ w[p + "k"].T).view(T, H, d)
+    v = _r(blend("v") @ w[p + "v"].T).view(T, H, d)
+    gate = silu(_r(blend("g") @ w[p + "g"].T))
+    decay = torch.exp(-torch.exp(_r(torch.tanh(blend("w") @ w[p + "w1"].T)) @ w[p + "w2"].T + w[p + "w0"])).view(T, H, d)
     bonus = w[p + "u"].view(H, d)
     S = torch.zeros(H, d, d, dtype=h.dtype)
     out = []
@@ -132,7 +139,7 @@ def wkv_mixer(h, w, p, m, eps):
         out.append(torch.einsum("hde,hd->he", S + bonus[:, :, None] * kv, r[t]))
         S = decay[t][:, :, None] * S + kv
     o = rms_norm(torch.stack(out), None, eps).reshape(T, H * d) * w[p + "norm"]
-    return (o * gate) @ w[p + "o"].T
+    return _r(o * gate) @ w[p + "o"].T
 
 
 # ---- feed-forward ---------------------------------------------------------------------------------
@@ -145,13 +152,13 @@ def routed_experts(h, w, p, f):
     for t in range(h.shape[0]):
         for j in range(top):
             e = f"{p}e{int(ids[t, j])}."
-            out[t] += weights[t, j] * ((silu(h[t] @ w[e + "gate"].T) * (h[t] @ w[e + "up"].T)) @ w[e + "down"].T)
+            out[t] += weights[t, j] * (_r(silu(h[t] @ w[e + "gate"].T) * (h[t] @ w[e + "up"].T)) @ w[e + "down"].T)
     return out
 
 
 def token_side_input(x, ids, w, p, index, dim, eps):
     e = w["side.embed"][ids][:, index * dim: (index + 1) * dim]
-    y = (gelu_tanh(x @ w[p + "gate"].T) * e) @ w[p + "proj"].T
+    y = _r(gelu_tanh(_r(x) @ w[p + "gate"].T) * e) @ w[p + "proj"].T
     return rms_norm(y, w[p + "norm"], eps)
 
 
@@ -168,8 +175,19 @@ def run_order(cfg):
     return order + [(i, None) for i in range(loop["stop"], n)]
 
 
-def forward(cfg, w, tokens, dtype=torch.float64, return_layers=False):
-    """Logits ``[T, vocab]`` of one sequence (and the stream after every run of a layer)."""
+def forward(cfg, w, tokens, dtype=torch.float64, return_layers=False, round_inputs=None):
+    """Logits ``[T, vocab]`` of one sequence (and the stream after every run of a layer).  ``round_inputs``: a dtype
+    through which every activation that passes from one matrix product to the next is rounded on its way (the
+    sublayers' inputs, projected queries, keys, values and gates, gated heads, hidden features), as a run that keeps
+    such activations in that dtype does: a measure of how far rounding alone moves a row.  Sums, norms, states and
+    scores stay as they are."""
+    global ROUND
+    if round_inputs is not None and ROUND is None:
+        ROUND = round_inputs
+        try:
+            return forward(cfg, w, tokens, dtype, return_layers, round_inputs)
+        finally:
+            ROUND = None
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in w.items()}
     eps = cfg["norm"]["eps"]
     ids = torch.as_tensor(list(tokens), dtype=torch.long)
@@ -177,6 +195,9 @@ def forward(cfg, w, tokens, dtype=torch.float64, return_layers=False):
     x = x0.clone()
     side = cfg.get("token_side")
     after = []
+
+    def rounded(h):
+        return h if round_inputs is None else h.to(round_inputs).to(dtype)
     for i, begins in run_order(cfg):
         if begins is not None:
             if begins > 0:
@@ -184,7 +205,7 @@ def forward(cfg, w, tokens, dtype=torch.float64, return_layers=False):
             x = x + w["loop.step"][begins]
         layer = cfg["layers"][i]
         p, m = f"l{i}.", layer["mixer"]
-        h = rms_norm(x, w[p + "norm1"], eps)
+        h = rounded(rms_norm(x, w[p + "norm1"], eps))
         if layer["type"] == "retention":
             y = retention_mixer(h, w, p + "mix.", m, eps)
         elif layer["type"] == "parallel":
@@ -195,12 +216,12 @@ def forward(cfg, w, tokens, dtype=torch.float64, return_layers=False):
             raise ValueError(layer["type"])
         x = x + rms_norm(y, w[p + "norm1b"], eps)
         if layer.get("mlp") is not None:
-            y = routed_experts(rms_norm(x, w[p + "norm2"], eps), w, p + "mlp.", layer["mlp"])
+            y = routed_experts(rounded(rms_norm(x, w[p + "norm2"], eps)), w, p + "mlp.", layer["mlp"])
             x = x + rms_norm(y, w[p + "norm2b"], eps)
         if side is not None:
             x = x + token_side_input(x, ids, w, p + "side.", i, side["dim"], eps)
         after.append(x)
-    logits = rms_norm(x, w["final.norm"], eps) @ w["head"].T
+    logits = rounded(rms_norm(x, w["final.norm"], eps)) @ w["head"].T
     cap = cfg.get("logit_softcap")
     if cap:
         logits = cap * torch.tanh(logits / cap)
