@@ -28,6 +28,8 @@ from a profiler's trace, bench/bench_kernels.py:71-116).
 mixed with a loop and routed experts) beside the two other designs at equal sizes.
 ``--only nukodra`` likewise: the Nukodra decoder (layers of one mixer kind each, on one residual stream and on
 four; then the kinds mixed) beside Zenedra's closest layers at equal sizes.
+``--only lunelorn`` likewise: the Lunelorn decoder (layers of one mixer kind each with routed experts, then the
+kinds mixed with a loop and the per-layer token input) beside Zenedra's closest layers at equal sizes.
 ``--only designs`` prints a line of its own: the Fakilorn decoder beside this decoder at equal width,
 depth, hidden width and vocabulary (random weights, two sizes): a 2,048-token prompt step, decode
 steps at the headline batch with contexts near 2,048, and the device time of every exported function
@@ -91,7 +93,7 @@ def parse_args():
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--page-tokens", type=int, default=64)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and prefill")
-    ap.add_argument("--only", choices=["all", "decode", "prefill", "serve", "kernels", "designs", "zenedra", "nukodra"], default="all",
+    ap.add_argument("--only", choices=["all", "decode", "prefill", "serve", "kernels", "designs", "zenedra", "nukodra", "lunelorn"], default="all",
                     help="a small case for profilers: only the device-timed decode steps, or only "
                          "the 2,048-token prefill (the printed line is then partial); serve: 64 "
                          "requests with prompts of 16 to 512 tokens and 256 generated tokens each "
@@ -681,6 +683,64 @@ def compare_nukodra(args) -> dict:
     return out
 
 
+# ``--only lunelorn``: the Lunelorn decoder beside Zenedra, the closest design here (matrix memories through the same
+# scan and chunk kernels, attention with a preparation kernel between projection and attention, routed experts, a
+# loop over layers), at equal width, depth, head count and vocabulary (random weights).  Layers of one mixer kind
+# each, so that every mixer's kernels can be read off alone: retention (half as many heads, values of 128, like
+# Zenedra's matrix memories), RWKV-style time mixing (heads of 64), attention with rotated unit values beside a
+# minGRU as wide as the model.  Feed-forwards are routed experts throughout (the design has no dense one); the rows
+# "no token input" leave the per-layer token embedding out.  Then the kinds mixed, two passes over the first layers.
+def _lunelorn_raw(sz: dict, kinds: list, side, loop: bool) -> dict:
+    heads = sz["heads"]
+    mixers = {
+        "retention": {"heads": heads // 2, "dim": 64, "vdim": 128,
+                      "decay": [1.0 - 2.0 ** (-5 - 5 * h / max(1, heads // 2 - 1)) for h in range(heads // 2)]},
+        "wkv": {"heads": sz["width"] // 64, "dim": 64},
+        "parallel": {"left": {"heads": heads, "kv_heads": sz["kv_heads"], "dim": 64, "vdim": 64, "scale": 0.125,
+                              "rot": {"dims": 64, "base": 10000.0}},
+                     "right": {"width": sz["width"]}, "left_scale": 1.0, "right_scale": 1.0},
+    }
+    routed = {"kind": "moe", "expert": {"ff": sz["expert_ff"]}, "router": {"experts": sz["experts"], "top": sz["top"]}}
+    layers = [{"type": kind, "mixer": dict(mixers[kind]), "mlp": routed} for kind in kinds]
+    raw = {"architecture": "Lunelorn", "vocab": sz["vocab"], "width": sz["width"], "layers": layers, "norm": {"eps": 1e-6},
+           "logit_softcap": 30.0}
+    if side:
+        raw["token_side"] = {"dim": side}
+    if loop:
+        raw["loop"] = {"start": 0, "stop": len(kinds) - 1, "times": 2}
+    return raw
+
+
+def compare_lunelorn(args) -> dict:
+    import torch
+
+    from mini_gpt_inference_b200 import LunelornConfig, ZenedraConfig
+    from mini_gpt_inference_b200.kernels.ops import default_ops
+
+    ops = default_ops("cuda:0")
+    batch, context, prompt_len = args.batch, 2048, PREFILL_TOKENS
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda:0")
+    out = {"impl": "ours", "partial": "lunelorn beside zenedra", "dtype": args.dtype, "batch": batch,
+           "context": context, "prompt": prompt_len, "rows": []}
+    for size_name, sz in DESIGN_SIZES.items():
+        n = sz["layers"]
+        for name, kinds, moe in (("attention, dense", ["attention"] * n, False), ("gla, dense", ["gla"] * n, False),
+                                 ("gla, dense+experts", ["gla"] * n, True)):
+            cfg = ZenedraConfig.from_dict(_zenedra_raw(sz, kinds, moe, False, context))
+            out["rows"].append(_measure_design(args, ops, flush, f"zenedra {size_name} {name}", cfg, batch, context,
+                                               prompt_len))
+        mixed = (["wkv", "retention", "parallel", "parallel"] * n)[:n]
+        for name, kinds, side, loop in (("retention, experts, no token input", ["retention"] * n, None, False),
+                                        ("wkv, experts, no token input", ["wkv"] * n, None, False),
+                                        ("parallel, experts, no token input", ["parallel"] * n, None, False),
+                                        ("retention, experts", ["retention"] * n, 128, False),
+                                        ("mixed, experts" + (", loop" if n >= 3 else ""), mixed, 128, n >= 3)):
+            cfg = LunelornConfig.from_dict(_lunelorn_raw(sz, kinds, side, loop))
+            out["rows"].append(_measure_design(args, ops, flush, f"lunelorn {size_name} {name}", cfg, batch, context,
+                                               prompt_len))
+    return out
+
+
 def check_decode_logits(args) -> dict:
     """Outside every timed region: the decode step that the benchmark times (batch 8, contexts of
     2,048, the replayed graph) is run once on fixed tokens and its logits are compared with rows
@@ -746,6 +806,8 @@ def run_ours(args) -> dict:
         return compare_zenedra(args)
     if args.only == "nukodra":
         return compare_nukodra(args)
+    if args.only == "lunelorn":
+        return compare_lunelorn(args)
     if args.only == "decode":
         cfg, windows, launches, mean_ctx, clocks = device_decode(args, args.batch, args.steps, args.warmup,
                                                                  min_seconds=0.0)

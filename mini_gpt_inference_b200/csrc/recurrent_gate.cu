@@ -10,6 +10,13 @@
 // time, the logistic functions) does not wait for the state.  The order of the sums is the tokens' order whatever
 // the cut into steps.
 //
+// gated_recurrence_ranges (long portions where the cut may move the last bits: bfloat16 steps): a CTA owns 32
+// channels of one request, its warps share the request's tokens in equal ranges.  The recurrence is affine in s, so
+// a range is the pair (keep, add) with s_out = keep * s_in + add: every warp scans its range once from s = 0 with
+// keep = prod (1 - z), the pairs meet in shared memory, a warp folds the pairs of the ranges before its own into its
+// incoming state, and scans its range again from there, writing the outputs.  The chain is two passes over a
+// range instead of one over the portion; state, gates and sums stay 32-bit.
+//
 // token_shift_mix: with h_t a token's input and h_(t-1) the input of the token before it in its sequence (zeros for a
 // sequence's first token; for a step's first token of a request it is read from the request's state slot),
 //   out[s][t] = h_t + (h_(t-1) - h_t) * mu[s]        for s = 0 .. n_mixes - 1
@@ -68,6 +75,77 @@ gated_recurrence_kernel(const float* __restrict__ pre, int ld, int z_off, int u_
     *s_ptr = s;
 }
 
+constexpr int RANGE_WARPS = 32;   // warps of a CTA of the range form
+
+template <typename T>
+__global__ void __launch_bounds__(32 * RANGE_WARPS)
+gated_recurrence_ranges_kernel(const float* __restrict__ pre, int ld, int z_off, int u_off, int g_off,
+                               const int* __restrict__ req_q_start, const int* __restrict__ req_q_len,
+                               const int* __restrict__ req_ctx_before, const int* __restrict__ req_state_slot,
+                               float* __restrict__ state, long long state_stride, T* __restrict__ out, int width,
+                               int n_slots, int n_tokens) {
+    __shared__ float keep_s[RANGE_WARPS][32], add_s[RANGE_WARPS][32];
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c = blockIdx.x * 32 + lane;
+    const int q_len = req_q_len[r];
+    if (q_len <= 0) return;                                    // a padding row of a fixed-size batch
+    const int start = req_q_start[r];
+    int slot = req_state_slot[r];
+    if (!MG_GUARDED(recurrent_gate, MG_GUARD_ROW, slot, n_slots) ||
+        !MG_GUARDED(recurrent_gate, MG_GUARD_ROW, start + q_len - 1, n_tokens))
+        return;
+    const bool live = c < width;
+    const int per = (q_len + RANGE_WARPS - 1) / RANGE_WARPS;
+    const int t_begin = min(warp * per, q_len), t_end = min(t_begin + per, q_len);
+    const float* base = pre + (size_t)start * ld + (live ? c : 0);
+    float keep = 1.f, add = 0.f;
+    for (int t0 = t_begin; t0 < t_end; t0 += AHEAD) {
+        float zv[AHEAD], uv[AHEAD];
+#pragma unroll
+        for (int i = 0; i < AHEAD; ++i) {
+            const float* row = base + (size_t)min(t0 + i, t_end - 1) * ld;
+            zv[i] = row[z_off];
+            uv[i] = row[u_off];
+        }
+#pragma unroll
+        for (int i = 0; i < AHEAD; ++i) {
+            if (t0 + i >= t_end) break;
+            const float z = sigmoidf(zv[i]);
+            const float cand = uv[i] >= 0.f ? uv[i] + 0.5f : sigmoidf(uv[i]);
+            add = fmaf(z, cand - add, add);
+            keep *= 1.f - z;
+        }
+    }
+    keep_s[warp][lane] = keep;
+    add_s[warp][lane] = add;
+    __syncthreads();
+    float* s_ptr = state + (size_t)slot * state_stride + (live ? c : 0);
+    float s = (req_ctx_before[r] == 0 || !live) ? 0.f : *s_ptr;
+    for (int w = 0; w < warp; ++w) s = fmaf(keep_s[w][lane], s, add_s[w][lane]);
+    for (int t0 = t_begin; t0 < t_end; t0 += AHEAD) {
+        float zv[AHEAD], uv[AHEAD], gv[AHEAD];
+#pragma unroll
+        for (int i = 0; i < AHEAD; ++i) {
+            const float* row = base + (size_t)min(t0 + i, t_end - 1) * ld;
+            zv[i] = row[z_off];
+            uv[i] = row[u_off];
+            gv[i] = row[g_off];
+        }
+#pragma unroll
+        for (int i = 0; i < AHEAD; ++i) {
+            if (t0 + i >= t_end) break;
+            const float z = sigmoidf(zv[i]);
+            const float cand = uv[i] >= 0.f ? uv[i] + 0.5f : sigmoidf(uv[i]);
+            s = fmaf(z, cand - s, s);
+            if (live) out[(size_t)(start + t0 + i) * width + c] = from_float<T>(s * gv[i] * sigmoidf(gv[i]));
+        }
+    }
+    // the warp of the last range that holds tokens leaves the state
+    if (live && t_end == q_len && t_begin < t_end) *s_ptr = s;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(THREADS)
 token_shift_mix_kernel(const T* __restrict__ x, const float* __restrict__ mu, const int* __restrict__ token_request,
@@ -100,18 +178,31 @@ token_shift_mix_kernel(const T* __restrict__ x, const float* __restrict__ mu, co
 
 // pre: [n_tokens, ld] 32-bit rows holding z, u and g (width numbers each) at the three column offsets; req_*:
 // [n_requests] first row, tokens, tokens already in the cache, state slot; state: 32-bit, `state_stride` numbers
-// a slot, of which the first `width` (from `state`) are this recurrence's; out: [n_tokens, width].
+// a slot, of which the first `width` (from `state`) are this recurrence's; out: [n_tokens, width].  ranges: 1 for
+// the form whose warps share a request's tokens (sums in another order than token by token), 0 token by token.
 MG_API int mg_gated_recurrence(const float* pre, int ld, int z_off, int u_off, int g_off, const int* req_q_start,
                                const int* req_q_len, const int* req_ctx_before, const int* req_state_slot, float* state,
                                long long state_stride, void* out, int n_requests, int n_tokens, int width, int n_slots,
-                               int out_bf16, void* stream) {
+                               int out_bf16, int ranges, void* stream) {
     if (n_requests == 0 || n_tokens == 0) return MG_OK;
     MG_REQUIRE(n_requests > 0 && n_requests <= 65535 && n_tokens > 0 && width > 0 && n_slots > 0 && state_stride >= width,
                "gated recurrence: bad sizes");
     MG_REQUIRE(z_off >= 0 && u_off >= 0 && g_off >= 0 && z_off + width <= ld && u_off + width <= ld && g_off + width <= ld,
                "gated recurrence: columns outside the rows");
-    const dim3 grid(ceil_div(width, THREADS), n_requests);
     cudaStream_t s = (cudaStream_t)stream;
+    if (ranges) {                                              // long portions: the warps of a CTA share the tokens
+        const dim3 rgrid(ceil_div(width, 32), n_requests);
+        const cudaError_t er =
+            out_bf16 ? mg_launch(gated_recurrence_ranges_kernel<bf16>, rgrid, dim3(32 * RANGE_WARPS), 0, s, true, pre, ld, z_off,
+                                 u_off, g_off, req_q_start, req_q_len, req_ctx_before, req_state_slot, state, state_stride,
+                                 (bf16*)out, width, n_slots, n_tokens)
+                     : mg_launch(gated_recurrence_ranges_kernel<float>, rgrid, dim3(32 * RANGE_WARPS), 0, s, true, pre, ld, z_off,
+                                 u_off, g_off, req_q_start, req_q_len, req_ctx_before, req_state_slot, state, state_stride,
+                                 (float*)out, width, n_slots, n_tokens);
+        if (er != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "gated recurrence (ranges): %s", cudaGetErrorString(er));
+        return MG_OK;
+    }
+    const dim3 grid(ceil_div(width, THREADS), n_requests);
     const cudaError_t e =
         out_bf16 ? mg_launch(gated_recurrence_kernel<bf16>, grid, dim3(THREADS), 0, s, true, pre, ld, z_off, u_off, g_off,
                              req_q_start, req_q_len, req_ctx_before, req_state_slot, state, state_stride, (bf16*)out, width,

@@ -2,9 +2,10 @@
 // per-layer token input add to the 32-bit residual stream; all sums and statistics 32-bit.
 //
 // rmsnorm_add:  x += (y / sqrt(mean(y^2) + eps)) * (offset + w),  y = sa * a [+ sb * b]   (one warp a row; the
-//               sublayer's output a, or the weighted sum of two sublayers that ran side by side)
+//               sublayer's output a, or the weighted sum of two sublayers that ran side by side).  With `clear` the
+//               inputs are left as zeros: the buffer a sublayer added its output into serves the next sublayer as it is
 // add_rows:     x += [e] + v    (e: rows like x, or none; v: one row for all tokens)
-// scaled_sum:   x += sa * a + sb * b
+// scaled_sum:   x += sa * a + sb * b   (with `clear`, a and b are left as zeros)
 // softcap:      x <- cap * tanh(x / cap)
 // token_gate:   out[t, j] = gelu_tanh(g[t, j]) * table[token_t, off + j]   (a slice of a second embedding table as a
 //               gate's other factor; tokens that the step before sampled are taken from its ids, as in the embedding)
@@ -18,16 +19,19 @@ MG_GUARD_DECLARE(residual_norm)
 namespace {
 
 constexpr int NORM_WARPS = 4;
+constexpr int ROW_THREADS = 256;   // threads of the CTA that owns a row in the vector form
+constexpr int ROW_VECS = 8;        // float4 a thread holds: rows of up to 256 * 8 * 4 = 8,192 numbers
 
+// The general form: one warp a row, two passes over the row (any width).
 __global__ void __launch_bounds__(32 * NORM_WARPS)
-rmsnorm_add_kernel(float* __restrict__ x, const float* __restrict__ a, float sa, const float* __restrict__ b, float sb,
-                   const float* __restrict__ w, int rows, int width, float eps, float offset) {
+rmsnorm_add_kernel(float* __restrict__ x, float* __restrict__ a, float sa, float* __restrict__ b, float sb,
+                   const float* __restrict__ w, int rows, int width, float eps, float offset, int clear) {
     pdl_trigger();
     pdl_wait();
     const int row = blockIdx.x * NORM_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= rows) return;
-    const float* ar = a + (size_t)row * width;
-    const float* br = b ? b + (size_t)row * width : nullptr;
+    float* ar = a + (size_t)row * width;
+    float* br = b ? b + (size_t)row * width : nullptr;
     float sq = 0.f;
     for (int c = lane; c < width; c += 32) {
         const float y = br ? fmaf(sb, br[c], sa * ar[c]) : sa * ar[c];
@@ -38,6 +42,64 @@ rmsnorm_add_kernel(float* __restrict__ x, const float* __restrict__ a, float sa,
     for (int c = lane; c < width; c += 32) {
         const float y = br ? fmaf(sb, br[c], sa * ar[c]) : sa * ar[c];
         xr[c] += y * rstd * (offset + w[c]);
+        if (clear) {
+            ar[c] = 0.f;
+            if (br) br[c] = 0.f;
+        }
+    }
+}
+
+// The vector form: one CTA a row, the row's numbers asked for at once (16 bytes a load) and held in registers
+// between the statistics and the sum, so that a step of few rows is one trip to memory and not a chain of them.
+__global__ void __launch_bounds__(ROW_THREADS)
+rmsnorm_add_vec_kernel(float* __restrict__ x, float* __restrict__ a, float sa, float* __restrict__ b, float sb,
+                       const float* __restrict__ w, int width, float eps, float offset, int clear) {
+    __shared__ float red[ROW_THREADS / 32];
+    pdl_trigger();
+    pdl_wait();
+    const int vecs = width >> 2, tid = threadIdx.x;
+    float4* ar = reinterpret_cast<float4*>(a + (size_t)blockIdx.x * width);
+    float4* br = b ? reinterpret_cast<float4*>(b + (size_t)blockIdx.x * width) : nullptr;
+    float4* xr = reinterpret_cast<float4*>(x + (size_t)blockIdx.x * width);
+    const float4* wr = reinterpret_cast<const float4*>(w);
+    float4 y[ROW_VECS], xv[ROW_VECS], wv[ROW_VECS];
+#pragma unroll
+    for (int u = 0; u < ROW_VECS; ++u) {
+        const int i = tid + u * ROW_THREADS;
+        y[u] = xv[u] = wv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < vecs) {
+            const float4 av = ar[i];
+            y[u] = make_float4(sa * av.x, sa * av.y, sa * av.z, sa * av.w);
+            if (br) {
+                const float4 bv = br[i];
+                y[u] = make_float4(fmaf(sb, bv.x, y[u].x), fmaf(sb, bv.y, y[u].y), fmaf(sb, bv.z, y[u].z), fmaf(sb, bv.w, y[u].w));
+            }
+            xv[u] = xr[i];
+            wv[u] = wr[i];
+        }
+    }
+    float sq = 0.f;
+#pragma unroll
+    for (int u = 0; u < ROW_VECS; ++u) sq = fmaf(y[u].x, y[u].x, fmaf(y[u].y, y[u].y, fmaf(y[u].z, y[u].z, fmaf(y[u].w, y[u].w, sq))));
+    sq = warp_sum(sq);
+    if ((tid & 31) == 0) red[tid >> 5] = sq;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int k = 0; k < ROW_THREADS / 32; ++k) total += red[k];
+    const float rstd = 1.0f / sqrtf(total / (float)width + eps);
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int u = 0; u < ROW_VECS; ++u) {
+        const int i = tid + u * ROW_THREADS;
+        if (i < vecs) {
+            xr[i] = make_float4(xv[u].x + y[u].x * rstd * (offset + wv[u].x), xv[u].y + y[u].y * rstd * (offset + wv[u].y),
+                                xv[u].z + y[u].z * rstd * (offset + wv[u].z), xv[u].w + y[u].w * rstd * (offset + wv[u].w));
+            if (clear) {
+                ar[i] = zero;
+                if (br) br[i] = zero;
+            }
+        }
     }
 }
 
@@ -52,12 +114,14 @@ __global__ void add_rows_kernel(float* __restrict__ x, const float* __restrict__
     x[i] = y;
 }
 
-__global__ void scaled_sum_kernel(float* __restrict__ x, const float* __restrict__ a, float sa,
-                                  const float* __restrict__ b, float sb, long long n) {
+__global__ void scaled_sum_kernel(float* __restrict__ x, float* __restrict__ a, float sa, float* __restrict__ b, float sb,
+                                  long long n, int clear) {
     pdl_trigger();
     pdl_wait();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) x[i] += fmaf(sb, b[i], sa * a[i]);
+    if (i >= n) return;
+    x[i] += fmaf(sb, b[i], sa * a[i]);
+    if (clear) a[i] = b[i] = 0.f;
 }
 
 __global__ void softcap_kernel(float* x, long long n, float cap) {
@@ -105,13 +169,18 @@ __global__ void token_gate_kernel(const float* __restrict__ g, const int* __rest
 
 }  // namespace
 
-// x: [rows, width] 32-bit, in place; a (and b, or null): [rows, width] 32-bit; w: [width] 32-bit.
-MG_API int mg_rmsnorm_add(float* x, const float* a, float sa, const float* b, float sb, const float* w, int rows,
-                          int width, float eps, float offset, void* stream) {
+// x: [rows, width] 32-bit, in place; a (and b, or null): [rows, width] 32-bit (zeroed if clear); w: [width] 32-bit.
+MG_API int mg_rmsnorm_add(float* x, float* a, float sa, float* b, float sb, const float* w, int rows,
+                          int width, float eps, float offset, int clear, void* stream) {
     if (rows == 0) return MG_OK;
     MG_REQUIRE(rows > 0 && width > 0 && x && a && w, "rmsnorm_add: bad sizes");
-    const cudaError_t e = mg_launch(rmsnorm_add_kernel, dim3(ceil_div(rows, NORM_WARPS)), dim3(32 * NORM_WARPS), 0,
-                                    (cudaStream_t)stream, true, x, a, sa, b, sb, w, rows, width, eps, offset);
+    const bool vec = width % 4 == 0 && width <= ROW_THREADS * ROW_VECS * 4 && (uintptr_t)x % 16 == 0 && (uintptr_t)a % 16 == 0 &&
+                     (uintptr_t)b % 16 == 0 && (uintptr_t)w % 16 == 0;
+    const cudaError_t e =
+        vec ? mg_launch(rmsnorm_add_vec_kernel, dim3(rows), dim3(ROW_THREADS), 0, (cudaStream_t)stream, true, x, a, sa, b, sb, w,
+                        width, eps, offset, clear)
+            : mg_launch(rmsnorm_add_kernel, dim3(ceil_div(rows, NORM_WARPS)), dim3(32 * NORM_WARPS), 0, (cudaStream_t)stream,
+                        true, x, a, sa, b, sb, w, rows, width, eps, offset, clear);
     if (e != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "rmsnorm_add: %s", cudaGetErrorString(e));
     return MG_OK;
 }
@@ -126,11 +195,11 @@ MG_API int mg_add_rows(float* x, const float* e, const float* v, long long n, in
     return MG_OK;
 }
 
-MG_API int mg_scaled_sum(float* x, const float* a, float sa, const float* b, float sb, long long n, void* stream) {
+MG_API int mg_scaled_sum(float* x, float* a, float sa, float* b, float sb, long long n, int clear, void* stream) {
     if (n == 0) return MG_OK;
     MG_REQUIRE(n > 0 && n < (1ll << 40) && a && b, "scaled_sum: bad sizes");
     const cudaError_t e = mg_launch(scaled_sum_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0,
-                                    (cudaStream_t)stream, true, x, a, sa, b, sb, n);
+                                    (cudaStream_t)stream, true, x, a, sa, b, sb, n, clear);
     if (e != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "scaled_sum: %s", cudaGetErrorString(e));
     return MG_OK;
 }

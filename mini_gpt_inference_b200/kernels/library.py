@@ -32,11 +32,11 @@ _SIGNATURES = {
     "mg_qk_norm_rotary": [_P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I,
                           _I, _F, _P, _P],
     "mg_rotate_heads": [_P, _I, _I, _I, _P, _P, _F, _I, _P],
-    "mg_gated_recurrence": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, ctypes.c_longlong, _P, _I, _I, _I, _I, _I, _P],
+    "mg_gated_recurrence": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, ctypes.c_longlong, _P, _I, _I, _I, _I, _I, _I, _P],
     "mg_token_shift_mix": [_P, _P, _P, _P, _P, _P, _P, _P, ctypes.c_longlong, _P, _I, _I, _I, _I, _I, _I, _P],
-    "mg_rmsnorm_add": [_P, _P, _F, _P, _F, _P, _I, _I, _F, _F, _P],
+    "mg_rmsnorm_add": [_P, _P, _F, _P, _F, _P, _I, _I, _F, _F, _I, _P],
     "mg_add_rows": [_P, _P, _P, ctypes.c_longlong, _I, _P],
-    "mg_scaled_sum": [_P, _P, _F, _P, _F, ctypes.c_longlong, _P],
+    "mg_scaled_sum": [_P, _P, _F, _P, _F, ctypes.c_longlong, _I, _P],
     "mg_softcap": [_P, ctypes.c_longlong, _F, _P],
     "mg_cast_rows": [_P, _P, ctypes.c_longlong, _I, _I, _P],
     "mg_token_gate": [_P, _P, _P, _P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _I, _I, _P],

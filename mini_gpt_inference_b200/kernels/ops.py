@@ -109,6 +109,7 @@ class CudaOps:
         self.use_prefill_tc = True
         self.use_mma_attention = True
         self.use_chunked_memory = True     # prompt portions of the matrix-memory mixers chunk by chunk (bfloat16)
+        self.use_recurrence_ranges = True  # long prompt portions of the gated recurrence with the warps sharing the tokens
         self.merge_ranges_in_last_cta = False
         self._counter_buf = None
         self._retired_counters = []
@@ -1120,7 +1121,9 @@ class CudaOps:
         """``s <- (1 - sigmoid(z)) s + sigmoid(z) cand(u)`` feature by feature over every request's tokens, from and to
         the requests' state slots (``width`` numbers from ``state_offset``); ``cand(u) = u + 1/2`` for ``u >= 0`` and
         ``sigmoid(u)`` below.  ``pre``: 32-bit rows with z, u and an output gate g at the three offsets.  Returns
-        ``s * silu(g)`` ``[tokens, width]`` in ``out_dtype``."""
+        ``s * silu(g)`` ``[tokens, width]`` in ``out_dtype``.  A bfloat16 step whose longest portion has
+        ``RECURRENCE_RANGE_MIN_TOKENS`` tokens or more runs the form whose warps share a request's tokens; 32-bit
+        steps always run token by token (one fixed order of sums whatever the cut)."""
         self._want(pre, torch.float32, "pre-activations", 2)
         self._want(state, torch.float32, "state slots", 2)
         if state_offset < 0 or state_offset + width > state.shape[1]:
@@ -1130,8 +1133,13 @@ class CudaOps:
         self._run(self.lib.mg_gated_recurrence(
             _ptr(pre), pre.shape[1], z_off, u_off, g_off, _ptr(ctx.req_q_start), _ptr(ctx.req_q_len), _ptr(ctx.req_ctx_before),
             _ptr(ctx.req_state_slot), state.data_ptr() + 4 * int(state_offset), state.shape[1], _ptr(out),
-            ctx.req_q_start.numel(), n, width, state.shape[0], self._is_bf16(out), self._stream()), "gated_recurrence")
+            ctx.req_q_start.numel(), n, width, state.shape[0], self._is_bf16(out),
+            1 if (out_dtype == torch.bfloat16 and self.use_recurrence_ranges
+                  and int(getattr(ctx, "max_q_len", 0)) >= self.RECURRENCE_RANGE_MIN_TOKENS) else 0,
+            self._stream()), "gated_recurrence")
         return out
+
+    RECURRENCE_RANGE_MIN_TOKENS = 128
 
     def token_shift_mix(self, ctx, x, mu, state):
         """``out[s] = x_t + (x_(t-1) - x_t) * mu[s]`` for every row of ``mu`` ``[mixes, width]`` (32-bit): ``[mixes, tokens,
@@ -1151,14 +1159,23 @@ class CudaOps:
         return out
 
     # ---- sums into the residual stream ------------------------------------------------------------------------
-    def zeros32(self, rows, width):
-        """A zeroed 32-bit buffer a sublayer can add its output into."""
+    def zeros32(self, rows, width, ctx=None, index=0):
+        """A zeroed 32-bit buffer a sublayer can add its output into.  With ``ctx``: buffer number ``index`` of the
+        forward pass that ``ctx`` belongs to, made and zeroed at its first use; whoever takes it leaves it as zeros
+        again (``rmsnorm_add`` and ``scaled_sum_`` with ``clear``), so one zero fill serves a whole pass."""
+        shared = getattr(ctx, "shared", None)
+        key = ("zeros32", rows, width, index)
+        if shared is not None and key in shared:
+            return shared[key]
         out = torch.empty((rows, width), dtype=torch.float32, device=self.device)
         self._run(self.lib.mg_zero_fill(_ptr(out), out.numel() * 4, self._stream()), "zero fill")
+        if shared is not None:
+            shared[key] = out
         return out
 
-    def rmsnorm_add(self, residual32, y32, weight, eps, offset=0.0, other32=None, scale=1.0, other_scale=1.0):
-        """``residual32 += rms_norm(scale * y32 [+ other_scale * other32]) * (offset + weight)``, in place, 32-bit."""
+    def rmsnorm_add(self, residual32, y32, weight, eps, offset=0.0, other32=None, scale=1.0, other_scale=1.0, clear=False):
+        """``residual32 += rms_norm(scale * y32 [+ other_scale * other32]) * (offset + weight)``, in place, 32-bit.
+        ``clear``: ``y32`` (and ``other32``) are left as zeros, ready for the next sublayer to add into."""
         self._want(residual32, torch.float32, "residual", 2)
         self._want(y32, torch.float32, "sublayer output", 2)
         self._want(weight, torch.float32, "norm weight", 1)
@@ -1168,7 +1185,7 @@ class CudaOps:
             raise KernelLibraryError("rmsnorm_add: shapes do not fit")
         self._run(self.lib.mg_rmsnorm_add(_ptr(residual32), _ptr(y32), float(scale), _ptr(other32), float(other_scale),
                                           _ptr(weight), residual32.shape[0], residual32.shape[1], float(eps), float(offset),
-                                          self._stream()), "rmsnorm_add")
+                                          1 if clear else 0, self._stream()), "rmsnorm_add")
         return residual32
 
     def add_rows(self, x32, rows32, vector):
@@ -1183,14 +1200,14 @@ class CudaOps:
                   "add_rows")
         return x32
 
-    def scaled_sum_(self, x32, a32, scale_a, b32, scale_b):
-        """``x32 += scale_a * a32 + scale_b * b32`` in place, 32-bit."""
+    def scaled_sum_(self, x32, a32, scale_a, b32, scale_b, clear=False):
+        """``x32 += scale_a * a32 + scale_b * b32`` in place, 32-bit.  ``clear``: ``a32`` and ``b32`` are left as zeros."""
         for name, t in (("sum", x32), ("first term", a32), ("second term", b32)):
             self._want(t, torch.float32, name, 2)
         if a32.shape != x32.shape or b32.shape != x32.shape:
             raise KernelLibraryError("scaled_sum: shapes do not fit")
         self._run(self.lib.mg_scaled_sum(_ptr(x32), _ptr(a32), float(scale_a), _ptr(b32), float(scale_b), x32.numel(),
-                                         self._stream()), "scaled_sum")
+                                         1 if clear else 0, self._stream()), "scaled_sum")
         return x32
 
     def softcap_(self, x32, cap: float):
@@ -1214,6 +1231,25 @@ class CudaOps:
         out = torch.empty(x32.shape, dtype=out_dtype, device=self.device)
         self._run(self.lib.mg_cast_rows(_ptr(x32), _ptr(out), x32.numel(), 1, self._is_bf16(out), self._stream()), "tanh")
         return out
+
+    def token_side_residual(self, ctx, residual32, gate_weight, proj_weight, norm_weight, table, offset, eps, act_dtype):
+        """``g = gelu_tanh(gate_weight x) * table[token, offset : offset + dim]``, ``y = proj_weight g``,
+        ``residual32 += y / sqrt(mean(y^2) + eps) * norm_weight`` with ``x`` the rows of ``residual32`` themselves, in
+        place: two projections with the gate between and the norm behind them.  ``x`` and ``g`` are rounded to
+        ``act_dtype`` on their way into the products; everything else is 32-bit.  (The whole of it as one kernel, a
+        CTA a token, was measured for steps of few tokens: 37 us a layer where these kernels take 14 inside a
+        replayed graph, because a token's CTA pulls both matrices through one SM.)"""
+        self._want(residual32, torch.float32, "residual", 2)
+        self._want(gate_weight, act_dtype, "gate matrix", 2)
+        self._want(proj_weight, act_dtype, "projection matrix", 2)
+        n, width = residual32.shape
+        dim = gate_weight.shape[0]
+        if gate_weight.shape != (dim, width) or proj_weight.shape != (width, dim):
+            raise KernelLibraryError("token_side: shapes do not fit")
+        gate = self.linear(self.cast(residual32, act_dtype), gate_weight, None, "none", torch.float32)
+        gated = self.token_gate(ctx, gate, table, offset, act_dtype)
+        y = self.linear(gated, proj_weight, None, "none", torch.float32)
+        return self.rmsnorm_add(residual32, y, norm_weight, eps)
 
     def token_gate(self, ctx, gate32, table, offset, out_dtype):
         """``gelu_tanh(gate32) * table[token, offset : offset + dim]``, ``dim`` the width of ``gate32``, in ``out_dtype``

@@ -93,14 +93,14 @@ register_arrangement("pre_norm_mixer_only")(pre_norm_mixer_only)
 def sandwich_norm(ctx, layer: Layer, cache, residual32):
     x = residual32
     rows, width = x.shape
-    zeros = ctx.ops.zeros32(rows, width)
+    # one zeroed buffer serves every sublayer of the pass: the norm behind a sublayer leaves it as zeros again
+    zeros = ctx.ops.zeros32(rows, width, ctx)
     y = stream_after(layer.mixer.forward(ctx, cache, _normed(ctx, layer.norm1, layer.mixer, x), zeros), zeros)
-    layer.norm1b.add_normed(ctx, y, x)
+    layer.norm1b.add_normed(ctx, y, x, clear=y is zeros)
     ff = layer.get("feed_forward")
     if ff is not None:
-        zeros = ctx.ops.zeros32(rows, width)
         y = stream_after(ff.forward(ctx, _normed(ctx, layer.norm2, ff, x), zeros), zeros)
-        layer.norm2b.add_normed(ctx, y, x)
+        layer.norm2b.add_normed(ctx, y, x, clear=y is zeros)
     side = layer.get("side_input")
     if side is not None:
         side.forward(ctx, x)

@@ -96,9 +96,10 @@ class ParallelMixers(Mixer):
     def forward(self, ctx, cache, y, residual32) -> None:
         ops = ctx.ops
         rows, width = residual32.shape
-        outs = []
-        for child in self.children:
-            zeros = ops.zeros32(rows, width)
+        outs, own = [], True
+        for index, child in enumerate(self.children):
+            zeros = ops.zeros32(rows, width, ctx, 1 + index)           # (buffer 0 is the layer arrangement's)
             held = child.forward(ctx, cache, y, zeros)
+            own = own and held is None
             outs.append(zeros if held is None else held)
-        ops.scaled_sum_(residual32, outs[0], self.scales[0], outs[1], self.scales[1])
+        ops.scaled_sum_(residual32, outs[0], self.scales[0], outs[1], self.scales[1], clear=own)

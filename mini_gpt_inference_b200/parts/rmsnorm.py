@@ -32,9 +32,10 @@ class RMSNorm(Norm):
     def forward(self, ctx, x32):
         return ctx.ops.rmsnorm(x32, self.weight, self.eps, self.offset, ctx.act_dtype)
 
-    def add_normed(self, ctx, y32, residual32):
-        """``residual32 += norm(y32)`` in 32-bit, in place: the norm behind a sublayer."""
-        return ctx.ops.rmsnorm_add(residual32, y32, self.weight, self.eps, self.offset)
+    def add_normed(self, ctx, y32, residual32, clear=False):
+        """``residual32 += norm(y32)`` in 32-bit, in place: the norm behind a sublayer.  ``clear``: ``y32`` is left
+        as zeros (a buffer that the next sublayer adds into)."""
+        return ctx.ops.rmsnorm_add(residual32, y32, self.weight, self.eps, self.offset, clear=clear)
 
     def defer(self, ctx, x32, rows=None):
         if not hasattr(ctx.ops, "defer_rmsnorm"):

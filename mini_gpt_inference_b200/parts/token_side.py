@@ -43,8 +43,5 @@ class TokenSideInput(SideInput):
         self.gate, self.proj, self.norm = tensors.get(p + "gate"), tensors.get(p + "proj"), tensors.get(p + "norm")
 
     def forward(self, ctx, residual32) -> None:
-        ops = ctx.ops
-        gate = ops.linear(ops.cast(residual32, ctx.act_dtype), self.gate, None, "none", residual32.dtype)
-        gated = ops.token_gate(ctx, gate, self.table, self.index * self.dim, ctx.act_dtype)
-        y = ops.linear(gated, self.proj, None, "none", residual32.dtype)
-        ops.rmsnorm_add(residual32, y, self.norm, self.eps)
+        ctx.ops.token_side_residual(ctx, residual32, self.gate, self.proj, self.norm, self.table, self.index * self.dim,
+                                    self.eps, ctx.act_dtype)

@@ -57,7 +57,7 @@ def batch(q_len, ctx_before, slots, tokens=None):
     return SimpleNamespace(req_q_start=ints(starts), req_q_len=ints(q_len), req_ctx_before=ints(ctx_before),
                            req_state_slot=ints(slots), token_request=ints(request), positions=ints(positions),
                            token_ids=ints(tokens if tokens is not None else [0] * n), num_requests=len(q_len),
-                           token_source=None, fed_ids=None, extra={})
+                           token_source=None, fed_ids=None, extra={}, max_q_len=max(q_len))
 
 
 # ---- the new kernels alone ---------------------------------------------------------------------------------------
@@ -71,6 +71,13 @@ def test_norm_behind_a_sublayer_and_the_sums_into_the_stream(ops, rows, width):
     got = ops.rmsnorm_add(dev(x), dev(a), dev(w), 1e-6, other32=dev(b), scale=1.2, other_scale=-0.5)
     assert torch.allclose(got.double().cpu(), x.double() + plain.rms_norm(1.2 * a.double() - 0.5 * b.double(), w.double(), 1e-6), atol=1e-5)
     assert torch.allclose(ops.scaled_sum_(dev(x), dev(a), 0.7, dev(b), 2.0).cpu(), x + 0.7 * a + 2.0 * b, atol=1e-5)
+    # with `clear` the inputs come back as zeros, the results are the same
+    xa, ya, yb = dev(x), dev(a), dev(b)
+    assert torch.equal(ops.rmsnorm_add(xa, ya, dev(w), 1e-6, other32=yb, scale=1.2, other_scale=-0.5, clear=True), got)
+    assert not bool(ya.any()) and not bool(yb.any())
+    ya, yb = dev(a), dev(b)
+    assert torch.allclose(ops.scaled_sum_(dev(x), ya, 0.7, yb, 2.0, clear=True).cpu(), x + 0.7 * a + 2.0 * b, atol=1e-5)
+    assert not bool(ya.any()) and not bool(yb.any())
     assert torch.allclose(ops.add_rows(dev(x), dev(a), dev(w)).cpu(), x + a + w, atol=1e-6)
     assert torch.allclose(ops.add_rows(dev(x), None, dev(w)).cpu(), x + w, atol=1e-6)
     assert torch.allclose(ops.softcap_(dev(10 * x), 7.0).cpu(), 7.0 * torch.tanh(10 * x / 7.0), atol=1e-5)
@@ -103,6 +110,29 @@ def test_gated_slice_of_the_token_table(ops, dtype, dim, parts):
     want = plain.gelu_tanh(gate.double()) * table.double()[fed][:, :dim]
     want[3] = 0
     assert torch.allclose(got.double(), want, atol=1e-5 if dtype == "float32" else 3e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("width,dim,index,tokens", [(64, 12, 1, 5), (192, 24, 3, 16), (1024, 128, 0, 8), (96, 8, 2, 40)])
+def test_token_input_of_a_layer(ops, dtype, width, dim, index, tokens):
+    """The gate's projection of the stream itself, the token's slice, the projection back and the norm, against the
+    plain function; a padding row stays as it is."""
+    t = DTYPES[dtype]
+    gen = torch.Generator().manual_seed(width + dim)
+    vocab = 40
+    w = {"side.embed": torch.randn(vocab, 4 * dim, generator=gen), "gate": torch.randn(dim, width, generator=gen) / math.sqrt(width),
+         "proj": torch.randn(width, dim, generator=gen) / math.sqrt(dim), "norm": 1 + 0.3 * torch.randn(width, generator=gen)}
+    w = {k: v.to(t).float() for k, v in w.items()}
+    x = 3 * torch.randn(tokens, width, generator=gen)
+    ids = torch.randint(0, vocab, (tokens,), generator=gen)
+    ctx = batch([tokens], [0], [0], ids.tolist())
+    ctx.positions[2] = -1
+    want = x.double() + plain.token_side_input(x.to(t).double(), ids, {k: v.double() for k, v in w.items()}, "", index, dim, 1e-5)
+    got = ops.token_side_residual(ctx, dev(x), dev(w["gate"], t), dev(w["proj"], t), dev(w["norm"]), dev(w["side.embed"], t),
+                                  index * dim, 1e-5, t)
+    live = [i for i in range(tokens) if i != 2]
+    assert torch.allclose(got.double().cpu()[live], want[live], atol=2e-5 if dtype == "float32" else 4e-2, rtol=1e-2)
+    assert torch.equal(got.cpu()[2], x[2])
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -140,12 +170,12 @@ def test_blend_with_the_token_before_across_steps(ops, dtype):
 def test_gated_recurrence_in_portions(ops, dtype, width):
     t = DTYPES[dtype]
     gen = torch.Generator().manual_seed(width)
-    lengths = [150, 9]
+    lengths = [300, 9]      # (bfloat16: the portion of 200 runs with the warps sharing its tokens, the others token by token)
     pre = [torch.randn(n, 3 * width + 4, generator=gen) * 3.0 for n in lengths]        # gates that open and shut
     offset = 6
     state = dev(torch.full((2, width + offset), float("nan")))
     pos, got = [0, 0], [[], []]
-    for portions in ([100, 2], [1, 1], [2, 6], [47, 0]):
+    for portions in ([200, 2], [1, 1], [2, 6], [97, 0]):
         live = [r for r in (0, 1) if portions[r]]
         rows = torch.cat([pre[r][pos[r]: pos[r] + portions[r]] for r in live])
         ctx = batch([portions[r] for r in live], [pos[r] for r in live], [r for r in live])

@@ -528,20 +528,35 @@ class TorchOps:
         cur = x.float()
         return (cur[None] + (before - cur)[None] * mu.float()[:, None, :]).to(x.dtype)
 
-    def zeros32(self, rows, width):
-        return torch.zeros(rows, width)
+    def zeros32(self, rows, width, ctx=None, index=0):
+        shared = getattr(ctx, "shared", None)
+        key = ("zeros32", rows, width, index)
+        if shared is not None and key in shared:
+            assert not bool(shared[key].any()), "a buffer of zeros was handed back with something in it"
+            return shared[key]
+        out = torch.zeros(rows, width)
+        if shared is not None:
+            shared[key] = out
+        return out
 
-    def rmsnorm_add(self, residual32, y32, weight, eps, offset=0.0, other32=None, scale=1.0, other_scale=1.0):
+    def rmsnorm_add(self, residual32, y32, weight, eps, offset=0.0, other32=None, scale=1.0, other_scale=1.0, clear=False):
         y = scale * y32 if other32 is None else scale * y32 + other_scale * other32
         residual32 += y / torch.sqrt((y * y).mean(-1, keepdim=True) + eps) * (offset + weight)
+        if clear:
+            y32.zero_()
+            if other32 is not None:
+                other32.zero_()
         return residual32
 
     def add_rows(self, x32, rows32, vector):
         x32 += vector if rows32 is None else rows32 + vector
         return x32
 
-    def scaled_sum_(self, x32, a32, scale_a, b32, scale_b):
+    def scaled_sum_(self, x32, a32, scale_a, b32, scale_b, clear=False):
         x32 += scale_a * a32 + scale_b * b32
+        if clear:
+            a32.zero_()
+            b32.zero_()
         return x32
 
     def softcap_(self, x32, cap):
@@ -553,6 +568,12 @@ class TorchOps:
 
     def tanh_cast(self, x32, out_dtype):
         return torch.tanh(x32).to(out_dtype)
+
+    def token_side_residual(self, ctx, residual32, gate_weight, proj_weight, norm_weight, table, offset, eps, act_dtype):
+        gate = self.linear(self.cast(residual32, act_dtype), gate_weight, None, "none", torch.float32)
+        gated = self.token_gate(ctx, gate, table, offset, act_dtype)
+        y = self.linear(gated, proj_weight, None, "none", torch.float32)
+        return self.rmsnorm_add(residual32, y, norm_weight, eps)
 
     def token_gate(self, ctx, gate32, table, offset, out_dtype):
         dim = gate32.shape[1]
