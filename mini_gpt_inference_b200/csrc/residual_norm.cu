@@ -20,7 +20,7 @@ namespace {
 
 constexpr int NORM_WARPS = 4;
 constexpr int ROW_THREADS = 256;   // threads of the CTA that owns a row in the vector form
-constexpr int ROW_VECS = 8;        // float4 a thread holds: rows of up to 256 * 8 * 4 = 8,192 numbers
+constexpr int MAX_ROW_VECS = 8;    // most float4 a thread holds: rows of up to 256 * 8 * 4 = 8,192 numbers
 
 // The general form: one warp a row, two passes over the row (any width).
 __global__ void __launch_bounds__(32 * NORM_WARPS)
@@ -51,6 +51,7 @@ rmsnorm_add_kernel(float* __restrict__ x, float* __restrict__ a, float sa, float
 
 // The vector form: one CTA a row, the row's numbers asked for at once (16 bytes a load) and held in registers
 // between the statistics and the sum, so that a step of few rows is one trip to memory and not a chain of them.
+template <int ROW_VECS>       // float4 a thread holds: 1, 2, 4 or 8 (rows of up to 1,024 ... 8,192 numbers)
 __global__ void __launch_bounds__(ROW_THREADS)
 rmsnorm_add_vec_kernel(float* __restrict__ x, float* __restrict__ a, float sa, float* __restrict__ b, float sb,
                        const float* __restrict__ w, int width, float eps, float offset, int clear) {
@@ -174,10 +175,13 @@ MG_API int mg_rmsnorm_add(float* x, float* a, float sa, float* b, float sb, cons
                           int width, float eps, float offset, int clear, void* stream) {
     if (rows == 0) return MG_OK;
     MG_REQUIRE(rows > 0 && width > 0 && x && a && w, "rmsnorm_add: bad sizes");
-    const bool vec = width % 4 == 0 && width <= ROW_THREADS * ROW_VECS * 4 && (uintptr_t)x % 16 == 0 && (uintptr_t)a % 16 == 0 &&
+    const bool vec = width % 4 == 0 && width <= ROW_THREADS * MAX_ROW_VECS * 4 && (uintptr_t)x % 16 == 0 && (uintptr_t)a % 16 == 0 &&
                      (uintptr_t)b % 16 == 0 && (uintptr_t)w % 16 == 0;
+    const int per_thread = ceil_div(width / 4, ROW_THREADS);
+    auto vec_kernel = per_thread <= 1 ? rmsnorm_add_vec_kernel<1> : per_thread <= 2 ? rmsnorm_add_vec_kernel<2>
+                    : per_thread <= 4 ? rmsnorm_add_vec_kernel<4> : rmsnorm_add_vec_kernel<8>;
     const cudaError_t e =
-        vec ? mg_launch(rmsnorm_add_vec_kernel, dim3(rows), dim3(ROW_THREADS), 0, (cudaStream_t)stream, true, x, a, sa, b, sb, w,
+        vec ? mg_launch(vec_kernel, dim3(rows), dim3(ROW_THREADS), 0, (cudaStream_t)stream, true, x, a, sa, b, sb, w,
                         width, eps, offset, clear)
             : mg_launch(rmsnorm_add_kernel, dim3(ceil_div(rows, NORM_WARPS)), dim3(32 * NORM_WARPS), 0, (cudaStream_t)stream,
                         true, x, a, sa, b, sb, w, rows, width, eps, offset, clear);

@@ -136,11 +136,12 @@ def test_token_input_of_a_layer(ops, dtype, width, dim, index, tokens):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_blend_with_the_token_before_across_steps(ops, dtype):
+@pytest.mark.parametrize("width", [72, 70, 1024])
+def test_blend_with_the_token_before_across_steps(ops, dtype, width):
     """Two requests in unequal portions: the row before a portion's first row comes from the state slot, zeros for a
-    sequence's first token; slots start as NaN."""
+    sequence's first token; slots start as NaN.  (Widths that the 16-byte form takes, and one that it does not.)"""
     t = DTYPES[dtype]
-    width, mixes = 72, 5
+    mixes = 5
     gen = torch.Generator().manual_seed(1)
     mu = torch.rand(mixes, width, generator=gen)
     seqs = [torch.randn(13, width, generator=gen).to(t), torch.randn(6, width, generator=gen).to(t)]
