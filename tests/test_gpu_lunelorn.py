@@ -113,7 +113,7 @@ def test_gated_slice_of_the_token_table(ops, dtype, dim, parts):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("width,dim,index,tokens", [(64, 12, 1, 5), (192, 24, 3, 16), (1024, 128, 0, 8), (96, 8, 2, 40)])
+@pytest.mark.parametrize("width,dim,index,tokens", [(64, 12, 1, 5), (160, 40, 3, 16), (1024, 128, 0, 8), (96, 8, 2, 40)])
 def test_token_input_of_a_layer(ops, dtype, width, dim, index, tokens):
     """The gate's projection of the stream itself, the token's slice, the projection back and the norm, against the
     plain function; a padding row stays as it is."""
