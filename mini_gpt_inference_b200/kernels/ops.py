@@ -36,8 +36,14 @@ class DeferredNorm:
         self.ops, self.x32, self.gain, self.shift, self.eps = ops, x32, gain, shift, float(eps)
         self.dtype, self.rows = out_dtype, rows
         self.shape = (x32.shape[0] if rows is None else rows.numel(), x32.shape[1])
+        self._rows_out = None      # the normalised rows, once a consumer asked for them (two consumers share them)
 
     def materialize(self):
+        if self._rows_out is None:
+            self._rows_out = self._materialize()
+        return self._rows_out
+
+    def _materialize(self):
         x = self.x32 if self.rows is None else self.ops.gather_rows(self.x32, self.rows)
         return self.ops.layernorm(x, self.gain, self.shift, self.eps, self.dtype)
 
@@ -50,7 +56,7 @@ class DeferredRMSNorm(DeferredNorm):
         super().__init__(ops, x32, gain, None, -abs(float(eps)), out_dtype, rows)
         self.weight, self.offset = weight, float(offset)
 
-    def materialize(self):
+    def _materialize(self):
         x = self.x32 if self.rows is None else self.ops.gather_rows(self.x32, self.rows)
         return self.ops.rmsnorm(x, self.weight, -self.eps, self.offset, self.dtype)
 

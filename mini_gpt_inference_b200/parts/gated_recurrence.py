@@ -59,7 +59,6 @@ class MinGRU(Mixer):
 
 @register_mixer("parallel_mixers")
 class ParallelMixers(Mixer):
-    accepts_deferred_norm = False      # two consumers read the normalised rows
 
     def __init__(self, prefix: str, left: dict, right: dict, left_scale: float = 1.0, right_scale: float = 1.0,
                  position=None) -> None:
@@ -68,6 +67,9 @@ class ParallelMixers(Mixer):
         self.children = [MIXERS.build(PartSpec(c["kind"], c["params"], name), prefix, position=position)
                          for name, c in (("left", left), ("right", right))]
         self.graph_safe = all(getattr(c, "graph_safe", False) for c in self.children)
+        # a norm that both sides can take into their first projection is handed on as it is: in steps of few tokens it
+        # rides in both projections' prologues, in longer ones it runs once (a deferred norm keeps its rows)
+        self.accepts_deferred_norm = all(getattr(c, "accepts_deferred_norm", False) for c in self.children)
 
     def tensor_specs(self):
         specs = {}
