@@ -47,6 +47,32 @@ def test_layers_with_equal_needs_share_a_group():
     assert m.state_layers == {4: FixedStateSpec((4, 4))}
 
 
+def test_a_layer_may_keep_pages_and_a_state_tensor():
+    """Pages and state at once: the pages join the group of layers with an equal page spec, the state is listed
+    beside them, and the layer's view of the storage carries both."""
+    import torch
+
+    from mini_gpt_inference_b200.cache.spec import PagedKVWithStateSpec
+    from mini_gpt_inference_b200.cache.storage import CacheStorage, PagedKVView, StateView
+
+    both = PagedKVWithStateSpec(PagedKVSpec(2, 16), FixedStateSpec((5,), "float32"))
+    m = CacheManager([PagedKVSpec(2, 16), both, FixedStateSpec((3,), "float32"), None, both], 4, 8, 2)
+    assert len(m.groups) == 1 and m.groups[0].layers == [0, 1, 4]
+    assert sorted(m.state_layers) == [1, 2, 4] and m.state_layers[1].shape == (5,)
+    storage = CacheStorage(m, torch.float32, "cpu")
+    plain, mixed, state, nothing = (storage.layer_view(i) for i in (0, 1, 2, 3))
+    assert isinstance(plain, PagedKVView) and plain.state is None
+    assert isinstance(mixed, PagedKVView) and mixed.state.shape == (2, 5) and mixed.k_pages.shape == (8, 2, 4, 16)
+    assert isinstance(state, StateView) and state.state.shape == (2, 3) and nothing is None
+    assert storage.layer_view(4).state is not mixed.state
+    m.admit("a")
+    m.reserve("a", 9)
+    m.advance("a", 9)
+    assert m.stats()["allocated_blocks"] == 3
+    m.release("a")
+    m.check()
+
+
 def test_reserve_grows_only_at_page_edges_and_is_all_or_nothing():
     m = _manager(num_pages=3, page_tokens=4)
     m.admit("a")
