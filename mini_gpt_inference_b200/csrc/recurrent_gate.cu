@@ -10,12 +10,13 @@
 // time, the logistic functions) does not wait for the state.  The order of the sums is the tokens' order whatever
 // the cut into steps.
 //
-// gated_recurrence_ranges (long portions where the cut may move the last bits: bfloat16 steps): a CTA owns 32
-// channels of one request, its warps share the request's tokens in equal ranges.  The recurrence is affine in s, so
-// a range is the pair (keep, add) with s_out = keep * s_in + add: every warp scans its range once from s = 0 with
-// keep = prod (1 - z), the pairs meet in shared memory, a warp folds the pairs of the ranges before its own into its
-// incoming state, and scans its range again from there, writing the outputs.  The chain is two passes over a
-// range instead of one over the portion; state, gates and sums stay 32-bit.
+// gated_recurrence_ranges (long portions where the cut may move the last bits: bfloat16 steps): a CTA owns 8
+// channels of one request (a quarter of a warp reads 32 bytes of a row: whole sectors) and its 128 quarter-warps
+// share the request's tokens in equal ranges, so that width / 8 CTAs fill the GPU at widths of a thousand and more.
+// The recurrence is affine in s, so a range is the pair (keep, add) with s_out = keep * s_in + add: every
+// quarter-warp scans its range once from s = 0 with keep = prod (1 - z), the pairs meet in shared memory, it folds
+// the pairs of the ranges before its own into its incoming state, and scans its range again from there, writing the
+// outputs.  The chain is two passes over a range instead of one over the portion; state, gates and sums stay 32-bit.
 //
 // token_shift_mix: with h_t a token's input and h_(t-1) the input of the token before it in its sequence (zeros for a
 // sequence's first token; for a step's first token of a request it is read from the request's state slot),
@@ -76,6 +77,8 @@ gated_recurrence_kernel(const float* __restrict__ pre, int ld, int z_off, int u_
 }
 
 constexpr int RANGE_WARPS = 32;   // warps of a CTA of the range form
+constexpr int RANGE_CH = 8;       // channels a CTA owns: a quarter of a warp
+constexpr int RANGES = RANGE_WARPS * (32 / RANGE_CH);   // token ranges a request is cut into
 
 template <typename T>
 __global__ void __launch_bounds__(32 * RANGE_WARPS)
@@ -84,11 +87,11 @@ gated_recurrence_ranges_kernel(const float* __restrict__ pre, int ld, int z_off,
                                const int* __restrict__ req_ctx_before, const int* __restrict__ req_state_slot,
                                float* __restrict__ state, long long state_stride, T* __restrict__ out, int width,
                                int n_slots, int n_tokens) {
-    __shared__ float keep_s[RANGE_WARPS][32], add_s[RANGE_WARPS][32];
+    __shared__ float keep_s[RANGES][RANGE_CH], add_s[RANGES][RANGE_CH];
     pdl_trigger();
     pdl_wait();
-    const int r = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int c = blockIdx.x * 32 + lane;
+    const int r = blockIdx.y, range = threadIdx.x / RANGE_CH, lane = threadIdx.x % RANGE_CH;
+    const int c = blockIdx.x * RANGE_CH + lane;
     const int q_len = req_q_len[r];
     if (q_len <= 0) return;                                    // a padding row of a fixed-size batch
     const int start = req_q_start[r];
@@ -97,8 +100,8 @@ gated_recurrence_ranges_kernel(const float* __restrict__ pre, int ld, int z_off,
         !MG_GUARDED(recurrent_gate, MG_GUARD_ROW, start + q_len - 1, n_tokens))
         return;
     const bool live = c < width;
-    const int per = (q_len + RANGE_WARPS - 1) / RANGE_WARPS;
-    const int t_begin = min(warp * per, q_len), t_end = min(t_begin + per, q_len);
+    const int per = (q_len + RANGES - 1) / RANGES;
+    const int t_begin = min(range * per, q_len), t_end = min(t_begin + per, q_len);
     const float* base = pre + (size_t)start * ld + (live ? c : 0);
     float keep = 1.f, add = 0.f;
     for (int t0 = t_begin; t0 < t_end; t0 += AHEAD) {
@@ -118,12 +121,12 @@ gated_recurrence_ranges_kernel(const float* __restrict__ pre, int ld, int z_off,
             keep *= 1.f - z;
         }
     }
-    keep_s[warp][lane] = keep;
-    add_s[warp][lane] = add;
+    keep_s[range][lane] = keep;
+    add_s[range][lane] = add;
     __syncthreads();
     float* s_ptr = state + (size_t)slot * state_stride + (live ? c : 0);
     float s = (req_ctx_before[r] == 0 || !live) ? 0.f : *s_ptr;
-    for (int w = 0; w < warp; ++w) s = fmaf(keep_s[w][lane], s, add_s[w][lane]);
+    for (int w = 0; w < range; ++w) s = fmaf(keep_s[w][lane], s, add_s[w][lane]);
     for (int t0 = t_begin; t0 < t_end; t0 += AHEAD) {
         float zv[AHEAD], uv[AHEAD], gv[AHEAD];
 #pragma unroll
@@ -142,7 +145,7 @@ gated_recurrence_ranges_kernel(const float* __restrict__ pre, int ld, int z_off,
             if (live) out[(size_t)(start + t0 + i) * width + c] = from_float<T>(s * gv[i] * sigmoidf(gv[i]));
         }
     }
-    // the warp of the last range that holds tokens leaves the state
+    // the last range that holds tokens leaves the state
     if (live && t_end == q_len && t_begin < t_end) *s_ptr = s;
 }
 
@@ -258,7 +261,7 @@ MG_API int mg_gated_recurrence(const float* pre, int ld, int z_off, int u_off, i
                "gated recurrence: columns outside the rows");
     cudaStream_t s = (cudaStream_t)stream;
     if (ranges) {                                              // long portions: the warps of a CTA share the tokens
-        const dim3 rgrid(ceil_div(width, 32), n_requests);
+        const dim3 rgrid(ceil_div(width, RANGE_CH), n_requests);
         const cudaError_t er =
             out_bf16 ? mg_launch(gated_recurrence_ranges_kernel<bf16>, rgrid, dim3(32 * RANGE_WARPS), 0, s, true, pre, ld, z_off,
                                  u_off, g_off, req_q_start, req_q_len, req_ctx_before, req_state_slot, state, state_stride,
